@@ -87,14 +87,15 @@ class _KVGroup:
     units: list            # schedule indices that own storage here
     pool: FreeList
     k: torch.Tensor        # [units, pages, Hkv, PAGE_SIZE, hd]
-    v: torch.Tensor
+    v: torch.Tensor | None # None for a spec without separate values
     pages: dict            # slot -> list of page ids, in order
 
 
 @dataclass
 class _StateUnit:
-    spec: StateSpec
-    storage: torch.Tensor  # [max_slots, *shape]
+    specs: tuple           # one StateSpec, or several
+    storages: tuple        # for each: [max_slots, *shape]
+    single: bool           # the mixer asked for one StateSpec (it sees the tensor itself, not a tuple)
 
 
 class CacheManager:
@@ -127,14 +128,16 @@ class CacheManager:
             if kv is not None:
                 by_spec.setdefault(kv, []).append(i)
             if state is not None:
-                storage = torch.zeros((max_slots, *state.shape), dtype=state.dtype, device=self.device)
-                self._unit_state[i] = _StateUnit(state, storage)
+                single = isinstance(state, StateSpec)
+                specs = (state,) if single else tuple(state)
+                storages = tuple(torch.zeros((max_slots, *sp.shape), dtype=sp.dtype, device=self.device) for sp in specs)
+                self._unit_state[i] = _StateUnit(specs, storages, single)
         for gid, (spec, members) in enumerate(by_spec.items()):
             shape = (len(members), self.n_pages, spec.n_kv_heads, PAGE_SIZE, spec.head_dim)
             # zeroed once (the reference zeroes its cache too, core/runtime.cpp:614-630): a page's unused tail is
             # multiplied by probability 0 in the tensor-core kernels and must hold finite numbers
             k = torch.zeros(shape, dtype=dtype, device=self.device)
-            v = torch.zeros(shape, dtype=dtype, device=self.device)
+            v = torch.zeros(shape, dtype=dtype, device=self.device) if spec.values else None
             self._groups.append(_KVGroup(spec, members, FreeList(self.n_pages, "page"), k, v, {}))
             for j, u in enumerate(members):
                 self._unit_group[u] = (gid, j)
@@ -152,17 +155,19 @@ class CacheManager:
         gid = k = v = state = None
         if owner in self._unit_group:
             gid, j = self._unit_group[owner]
-            k, v = self._groups[gid].k[j], self._groups[gid].v[j]
+            k = self._groups[gid].k[j]
+            v = self._groups[gid].v[j] if self._groups[gid].v is not None else None
         if owner in self._unit_state:
-            state = self._unit_state[owner].storage
+            st = self._unit_state[owner]
+            state = st.storages[0] if st.single else st.storages
         return UnitCache(gid, k, v, state, writable)
 
     def bytes_held(self) -> int:
         n = 0
         for g in self._groups:
-            n += (g.k.numel() + g.v.numel()) * g.k.element_size()
+            n += (g.k.numel() + (g.v.numel() if g.v is not None else 0)) * g.k.element_size()
         for s in self._unit_state.values():
-            n += s.storage.numel() * s.storage.element_size()
+            n += sum(t.numel() * t.element_size() for t in s.storages)
         return n
 
     # ------------------------------------------------------------------ slots
@@ -176,7 +181,9 @@ class CacheManager:
         if self._unit_state and slots:
             idx = torch.tensor(slots, dtype=torch.long, device=self.device)
             for st in self._unit_state.values():
-                st.storage.index_fill_(0, idx, 0)
+                for storage in st.storages:
+                    if storage.numel():
+                        storage.index_fill_(0, idx, 0)
         return slots
 
     def close(self, slots) -> None:

@@ -75,10 +75,11 @@ def model_info(config, dtype: str) -> dict:
     tensors = [t for t in model.tensors() if not (t.optional or t.ignored)]
     size = lambda dt: torch.empty((), dtype=dt).element_size()
     weight_bytes = sum(math.prod(t.shape) * size(held_dtype(t, compute, compute)) for t in tensors)
-    cache_bytes = sum(2 * kv.n_kv_heads * kv.head_dim * size(compute)
+    cache_bytes = sum((2 if kv.values else 1) * kv.n_kv_heads * kv.head_dim * size(compute)
                       for kv, _, cache_of in model.cache_units() if kv is not None and cache_of is None)
-    state_bytes = sum(math.prod(st.shape) * size(st.dtype)
-                      for _, st, cache_of in model.cache_units() if st is not None and cache_of is None)
+    state_bytes = sum(math.prod(sp.shape) * size(sp.dtype)
+                      for _, st, cache_of in model.cache_units() if st is not None and cache_of is None
+                      for sp in (st if isinstance(st, (tuple, list)) else (st,)))
     return {"config": config.to_dict(), "parameters": sum(math.prod(t.shape) for t in tensors), "layers": len(plan.layers),
             "tensors": len(plan.manifest()),
             "memory": {"dtype": dtype, "weight_bytes": weight_bytes, "cache_bytes_per_token": cache_bytes,

@@ -135,3 +135,8 @@ class ModelConfig:
 
     def to_dict(self) -> dict:
         raise NotImplementedError
+
+    def with_tensor_shapes(self, shapes: Mapping[str, tuple]) -> "ModelConfig":
+        """The configuration completed by sizes that only the weights' shapes give (``shapes``: tensor name -> shape).
+        Most architectures have none and return themselves."""
+        return self

@@ -48,6 +48,10 @@ def get_architecture(name: str) -> Architecture:
 
 
 def architecture_name(data: Mapping[str, Any], where: str = "config.json") -> str:
+    """The name a config.json files its model under: ``architectures`` (a list with one name), or ``architecture``
+    (the name itself)."""
+    if "architectures" not in data and isinstance(data.get("architecture"), str):
+        return data["architecture"]
     archs = data.get("architectures")
     if not isinstance(archs, list) or len(archs) != 1 or not isinstance(archs[0], str):
         raise ConfigError(f"{where}: key 'architectures' must be a list with one name, got {archs!r}")
@@ -61,6 +65,16 @@ def config_from_dict(data: Mapping[str, Any], where: str = "config.json") -> Mod
 
 
 def load_config(model_dir: str) -> ModelConfig:
+    """The folder's configuration; sizes that only the weights' shapes give are read from the weight files' headers
+    when the folder has some (``ModelConfig.with_tensor_shapes``)."""
     import os
     data = read_config_json(model_dir)
-    return config_from_dict(data, os.path.join(model_dir, "config.json"))
+    cfg = config_from_dict(data, os.path.join(model_dir, "config.json"))
+    if any(os.path.exists(os.path.join(model_dir, f)) for f in ("model.safetensors", "model.safetensors.index.json")):
+        from ..weights.safetensors_io import SafetensorsFolder
+        folder = SafetensorsFolder(model_dir)
+        try:
+            cfg = cfg.with_tensor_shapes({n: tuple(folder.info(n)[1]) for n in folder.names()})
+        finally:
+            folder.close()
+    return cfg

@@ -1,0 +1,253 @@
+// Latent attention: every head reads the same cached row per token, [latent c (L values) | rotated key part
+// (R values)], and that row's first L values are the value too.  A query head brings its query already taken
+// into the latent space (W_uk^T q, L values) and its rotated part (R values); the score is their dot product
+// with the cached row, times a scale; the output is the weighted sum of latents, which the caller takes through
+// W_uv.  Causal, with an optional window (key j is visible from position p when p - window < j <= p) and an
+// optional sink per head: one more term exp(sink) in the softmax's denominator that has no value.
+// Scores, maxima, sums and the accumulator are 32-bit; the queries come in 32-bit; the cache is float or bfloat16.
+//
+// Cache layout: pool [n_pages, page_size, L + R]; page_table [B, table_width].
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------
+// Preparation, one block per token:
+//   c = dkv[:L] / rms(dkv[:L]) * c_weight          -> cache row [:L]
+//   rotated key part: pairs (2i, 2i + 1) of dkv[L:] -> cache row [L:]  (values beyond 2 * half pass unchanged)
+//   q_rot[t, h, :] = the same rotation of q[t, h, K:]; q_plain[h, t, :] = q[t, h, :K] in the products' dtype
+// cos, sin [T, half] already hold any factor on them.
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void latent_prep_kernel(const float* __restrict__ q, const float* __restrict__ dkv, const float* __restrict__ c_weight,
+                                   const float* __restrict__ cosv, const float* __restrict__ sinv, const int* __restrict__ tok_seq,
+                                   const int* __restrict__ tok_pos, const int* __restrict__ page_table, T* __restrict__ pool,
+                                   T* __restrict__ q_plain, float* __restrict__ q_rot, int n_tok, int H, int K, int R, int L,
+                                   int half, float eps, int page_size, int table_width, int store) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const float* drow = dkv + (size_t)t * (L + R);
+    const float* cs = cosv + (size_t)t * half;
+    const float* sn = sinv + (size_t)t * half;
+    if (store) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < L; i += blockDim.x) ss += drow[i] * drow[i];
+        const float scale = rsqrtf(block_sum(ss, red) / (float)L + eps);
+        const int b = tok_seq[t], pos = tok_pos[t];
+        T* dst = pool + ((size_t)page_table[(size_t)b * table_width + pos / page_size] * page_size + pos % page_size) * (L + R);
+        for (int i = threadIdx.x; i < L; i += blockDim.x) dst[i] = from_f32<T>(drow[i] * scale * c_weight[i]);
+        for (int i = threadIdx.x; i < R; i += blockDim.x) {
+            float v = drow[L + i];
+            if (i < 2 * half) {
+                const float other = drow[L + (i ^ 1)], c = cs[i >> 1], s = sn[i >> 1];
+                v = (i & 1) ? v * c + other * s : v * c - other * s;
+            }
+            dst[L + i] = from_f32<T>(v);
+        }
+    }
+    const float* qrow = q + (size_t)t * H * (K + R);
+    for (int idx = threadIdx.x; idx < H * K; idx += blockDim.x) {
+        const int h = idx / K, d = idx - h * K;
+        q_plain[((size_t)h * n_tok + t) * K + d] = from_f32<T>(qrow[h * (K + R) + d]);
+    }
+    for (int idx = threadIdx.x; idx < H * R; idx += blockDim.x) {
+        const int h = idx / R, i = idx - h * R;
+        const float* src = qrow + h * (K + R) + K;
+        float v = src[i];
+        if (i < 2 * half) {
+            const float other = src[i ^ 1], c = cs[i >> 1], s = sn[i >> 1];
+            v = (i & 1) ? v * c + other * s : v * c - other * s;
+        }
+        q_rot[(size_t)t * H * R + idx] = v;
+    }
+}
+
+extern "C" int qwb_latent_prep(const float* q, const float* dkv, const float* c_weight, const float* cosv, const float* sinv,
+                               const int* tok_seq, const int* tok_pos, const int* page_table, void* pool, int dtype,
+                               void* q_plain, float* q_rot, int T, int H, int K, int R, int L, int half, float eps,
+                               int page_size, int table_width, int store, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || K <= 0 || R < 0 || L <= 0 || half < 0 || 2 * half > R)
+        return qwb_fail(QWB_ERR_ARG, "latent_prep: %d heads of %d + %d, latent %d, %d rotated pairs", H, K, R, L, half);
+    if (dtype == QWB_DT_F32)
+        qwb_launch(latent_prep_kernel<float>, T, 128, 0, stream, q, dkv, c_weight, cosv, sinv, tok_seq, tok_pos, page_table,
+                   (float*)pool, (float*)q_plain, q_rot, T, H, K, R, L, half, eps, page_size, table_width, store);
+    else if (dtype == QWB_DT_BF16)
+        qwb_launch(latent_prep_kernel<bf16>, T, 128, 0, stream, q, dkv, c_weight, cosv, sinv, tok_seq, tok_pos, page_table,
+                   (bf16*)pool, (bf16*)q_plain, q_rot, T, H, K, R, L, half, eps, page_size, table_width, store);
+    else
+        return qwb_fail(QWB_ERR_ARG, "latent_prep: unknown dtype %d", dtype);
+    return qwb_check_launch("latent_prep");
+}
+
+// ---------------------------------------------------------------------------------
+// Attention.  A block takes 16 rows, a row being a (token, head) pair: HB = min(H, 16) heads of TQ = 16 / HB
+// consecutive tokens of one sequence, so that the rows share the key tiles.  4 warps, 4 rows each; keys in tiles
+// of 32, one key per lane.  Prompts and single tokens are the same code (a single token is a tile of one token).
+//   q_abs [H, T, L] float, q_rot [T, H, R] float;  out [H, T, L] in the cache's dtype
+// ---------------------------------------------------------------------------------
+template <typename T, int NC>       // NC * 32 >= L
+__global__ void latent_attn_kernel(const float* __restrict__ q_abs, const float* __restrict__ q_rot, const T* __restrict__ pool,
+                                   const int* __restrict__ page_table, const int* __restrict__ cu_seqlens,
+                                   const int* __restrict__ pos0, const float* __restrict__ sink, T* __restrict__ out, int n_tok,
+                                   int H, int L, int R, int page_size, int table_width, float scale, int window) {
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int ROWS = 16, BK = 32, RPW = 4;
+    const int dk = L + R;
+    extern __shared__ float smem[];
+    float* Qs = smem;                       // [ROWS][dk], scaled
+    float* Ks = Qs + ROWS * dk;             // [BK][dk + 1]
+
+    const int HB = min(H, ROWS), TQ = ROWS / HB;
+    const int b = blockIdx.z, h0 = blockIdx.y * HB, q0 = blockIdx.x * TQ;
+    const int t0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - t0;
+    if (q0 >= n_new) return;
+    const int nq = min(TQ, n_new - q0), nh = min(HB, H - h0);
+    const int p0 = pos0[b];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    for (int idx = threadIdx.x; idx < ROWS * dk; idx += blockDim.x) {
+        const int r = idx / dk, d = idx - r * dk;
+        const int qi = r / HB, hi = r - qi * HB;
+        float v = 0.f;
+        if (qi < nq && hi < nh) {
+            const int t = t0 + q0 + qi, h = h0 + hi;
+            v = d < L ? q_abs[((size_t)h * n_tok + t) * L + d] : q_rot[((size_t)t * H + h) * R + (d - L)];
+        }
+        Qs[idx] = v * scale;
+    }
+
+    float m[RPW], l[RPW], acc[RPW][NC];
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+        m[i] = -INFINITY; l[i] = 0.f;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) acc[i][c] = 0.f;
+    }
+    const int k_last = p0 + q0 + nq - 1;
+    const int k_first = window > 0 ? max(0, p0 + q0 - window + 1) : 0;
+    const int* pages = page_table + (size_t)b * table_width;
+
+    for (int kt = (k_first / BK) * BK; kt <= k_last; kt += BK) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < BK * dk; idx += blockDim.x) {
+            const int j = idx / dk, d = idx - j * dk, key = kt + j;
+            float kv = 0.f;
+            if (key <= k_last) kv = to_f32(pool[((size_t)pages[key / page_size] * page_size + key % page_size) * dk + d]);
+            Ks[j * (dk + 1) + d] = kv;
+        }
+        __syncthreads();
+        float s[RPW];
+#pragma unroll
+        for (int i = 0; i < RPW; ++i) s[i] = 0.f;
+        const float* krow = Ks + lane * (dk + 1);
+        for (int d = 0; d < dk; ++d) {
+            const float kd = krow[d];
+#pragma unroll
+            for (int i = 0; i < RPW; ++i) s[i] += Qs[(warp * RPW + i) * dk + d] * kd;
+        }
+        const int key = kt + lane;
+        float p[RPW];
+#pragma unroll
+        for (int i = 0; i < RPW; ++i) {
+            const int r = warp * RPW + i;
+            const int qi = r / HB, hi = r - qi * HB;
+            const int qp = p0 + q0 + qi;
+            const bool ok = qi < nq && hi < nh && key <= qp && (window <= 0 || key > qp - window);
+            const float si = ok ? s[i] : -INFINITY;
+            const float m_new = fmaxf(m[i], warp_max(si));
+            if (m_new == -INFINITY) { p[i] = 0.f; continue; }
+            const float alpha = expf(m[i] - m_new);
+            p[i] = ok ? expf(si - m_new) : 0.f;
+            l[i] = l[i] * alpha + warp_sum(p[i]);
+            m[i] = m_new;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) acc[i][c] *= alpha;
+        }
+        for (int j = 0; j < BK; ++j) {
+            float pj[RPW];
+#pragma unroll
+            for (int i = 0; i < RPW; ++i) pj[i] = __shfl_sync(0xffffffffu, p[i], j);
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                const int d = lane + 32 * c;
+                if (d < L) {
+                    const float v = Ks[j * (dk + 1) + d];
+#pragma unroll
+                    for (int i = 0; i < RPW; ++i) acc[i][c] += pj[i] * v;
+                }
+            }
+        }
+    }
+
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+        const int r = warp * RPW + i;
+        const int qi = r / HB, hi = r - qi * HB;
+        if (qi >= nq || hi >= nh) continue;
+        const int h = h0 + hi;
+        float mi = m[i], li = l[i], rescale = 1.f;
+        if (sink) {                                             // one more term in the denominator, with no value
+            const float sk = sink[h];
+            const float m_new = fmaxf(mi, sk);
+            rescale = expf(mi - m_new);
+            li = li * rescale + expf(sk - m_new);
+        }
+        const float inv = rescale / li;
+        T* o = out + ((size_t)h * n_tok + t0 + q0 + qi) * L;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+            const int d = lane + 32 * c;
+            if (d < L) o[d] = from_f32<T>(acc[i][c] * inv);
+        }
+    }
+}
+
+template <typename T>
+static int launch_latent_attn(const float* q_abs, const float* q_rot, const void* pool, const int* page_table,
+                              const int* cu_seqlens, const int* pos0, const float* sink, void* out, int B, int n_tok,
+                              int max_new, int H, int L, int R, int page_size, int table_width, float scale, int window,
+                              cudaStream_t stream) {
+    const int dk = L + R;
+    const size_t smem = ((size_t)16 * dk + 32 * (dk + 1)) * sizeof(float);
+    const int HB = H < 16 ? H : 16, TQ = 16 / HB;
+    dim3 grid((max_new + TQ - 1) / TQ, (H + HB - 1) / HB, B);
+    const int nc = (L + 31) / 32;
+#define QWB_LAUNCH_LATENT(NC)                                                                                          \
+    do {                                                                                                               \
+        if (smem > 48 * 1024) {                                                                                        \
+            cudaError_t e = cudaFuncSetAttribute(latent_attn_kernel<T, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "latent_attn: %s", cudaGetErrorString(e));             \
+        }                                                                                                              \
+        qwb_launch(latent_attn_kernel<T, NC>, grid, 128, smem, stream, q_abs, q_rot, (const T*)pool, page_table,       \
+                   cu_seqlens, pos0, sink, (T*)out, n_tok, H, L, R, page_size, table_width, scale, window);            \
+    } while (0)
+    if (nc <= 2) QWB_LAUNCH_LATENT(2);
+    else if (nc <= 4) QWB_LAUNCH_LATENT(4);
+    else if (nc <= 8) QWB_LAUNCH_LATENT(8);
+    else QWB_LAUNCH_LATENT(16);
+#undef QWB_LAUNCH_LATENT
+    return qwb_check_launch("latent_attn");
+}
+
+#define QWB_LATENT_MAX_L 512
+#define QWB_LATENT_MAX_ROW 1024
+
+extern "C" int qwb_latent_attn(const float* q_abs, const float* q_rot, const void* pool, const int* page_table,
+                               const int* cu_seqlens, const int* pos0, const float* sink, void* out, int dtype, int B,
+                               int n_tok, int max_new, int H, int L, int R, int page_size, int table_width, float scale,
+                               int window, cudaStream_t stream) {
+    if (B <= 0 || n_tok <= 0 || max_new <= 0) return 0;
+    if (H <= 0 || L <= 0 || R < 0 || L > QWB_LATENT_MAX_L || L + R > QWB_LATENT_MAX_ROW)
+        return qwb_fail(QWB_ERR_ARG, "latent_attn: %d heads, latent %d (up to %d) + rotated %d (row up to %d)", H, L, QWB_LATENT_MAX_L, R, QWB_LATENT_MAX_ROW);
+    if (page_size <= 0 || table_width <= 0) return qwb_fail(QWB_ERR_ARG, "latent_attn: bad page size %d or table width %d", page_size, table_width);
+    if (B > 65535 || H > 65535 * 16) return qwb_fail(QWB_ERR_ARG, "latent_attn: batch %d or heads %d are too many", B, H);
+    if (dtype == QWB_DT_F32)
+        return launch_latent_attn<float>(q_abs, q_rot, pool, page_table, cu_seqlens, pos0, sink, out, B, n_tok, max_new, H, L, R,
+                                         page_size, table_width, scale, window, stream);
+    if (dtype == QWB_DT_BF16)
+        return launch_latent_attn<bf16>(q_abs, q_rot, pool, page_table, cu_seqlens, pos0, sink, out, B, n_tok, max_new, H, L, R,
+                                        page_size, table_width, scale, window, stream);
+    return qwb_fail(QWB_ERR_ARG, "latent_attn: unknown dtype %d", dtype);
+}

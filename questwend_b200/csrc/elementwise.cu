@@ -420,3 +420,85 @@ extern "C" int qwb_decode_advance(const int* sampled, int* token_ids, int* tok_p
                                                                step_counter, recent, n_seen, window, B);
     return qwb_check_launch("decode_advance");
 }
+
+// ---------------------------------------------------------------------------------
+// The norm on a sublayer's OUTPUT:  h[t, :] += y[t, :] * rsqrt(mean(y[t, :]^2) + eps) * w, in 32-bit and in place,
+// for blocks whose sublayers read the stream itself and whose results are normed before they join it.  `cast`
+// (optional, float or bfloat16) receives the new h in the dtype of the next product's operands.  One block per row;
+// the row of y stays in shared memory between the two passes.
+// ---------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void rmsnorm_onto_kernel(const float* __restrict__ y, const float* __restrict__ w, float* h, TOut* __restrict__ cast,
+                                    int D, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ __align__(16) float row_cache[];
+    __shared__ float red[32];
+    const size_t at = (size_t)blockIdx.x * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = y[at + i];
+        row_cache[i] = v;
+        ss += v * v;
+    }
+    const float scale = rsqrtf(block_sum(ss, red) / (float)D + eps);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = h[at + i] + row_cache[i] * scale * w[i];
+        h[at + i] = v;
+        if (cast) cast[at + i] = from_f32<TOut>(v);
+    }
+}
+
+extern "C" int qwb_rmsnorm_onto(const float* y, const float* w, float* h, void* cast, int cast_dtype, int T, int D, float eps,
+                                cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (D <= 0) return qwb_fail(QWB_ERR_ARG, "rmsnorm_onto: bad width %d", D);
+    const size_t smem = (size_t)D * sizeof(float);
+    if (smem > 200 * 1024) return qwb_fail(QWB_ERR_ARG, "rmsnorm_onto: width %d does not fit in shared memory", D);
+    const int block = D >= 1024 ? 256 : 128;
+    cudaError_t e = cudaSuccess;
+    if (cast && cast_dtype == QWB_DT_BF16) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_onto_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm_onto: %s", cudaGetErrorString(e));
+        qwb_launch(rmsnorm_onto_kernel<bf16>, T, block, smem, stream, y, w, h, (bf16*)cast, D, eps);
+    } else if (!cast || cast_dtype == QWB_DT_F32) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_onto_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm_onto: %s", cudaGetErrorString(e));
+        qwb_launch(rmsnorm_onto_kernel<float>, T, block, smem, stream, y, w, h, (float*)cast, D, eps);
+    } else {
+        return qwb_fail(QWB_ERR_ARG, "rmsnorm_onto: unknown dtype %d", cast_dtype);
+    }
+    return qwb_check_launch("rmsnorm_onto");
+}
+
+// ---------------------------------------------------------------------------------
+// out[t, f] = act(x[t, f] + bias[f]) for F columns of a float matrix with rows of ld values (the caller offsets the
+// pointer to the first column); out [T, F] float or bfloat16 (may be x itself when float and ld = F).
+// act 0: none; 1: relu squared; 2: gelu (tanh form); 3: silu.  bias may be null.
+// ---------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void bias_act_kernel(const float* x, int ld, const float* __restrict__ bias, TOut* out, size_t n, int F, int act) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / F, f = i - t * F;
+        float v = x[t * ld + f] + (bias ? bias[f] : 0.f);
+        if (act == 1) { v = fmaxf(v, 0.f); v *= v; }
+        else if (act == 2) v = 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+        else if (act == 3) v = v / (1.f + expf(-v));
+        out[i] = from_f32<TOut>(v);
+    }
+}
+
+extern "C" int qwb_bias_act(const float* x, int ld, const float* bias, void* out, int out_dtype, int T, int F, int act, cudaStream_t stream) {
+    if (T <= 0 || F <= 0) return 0;
+    if (ld < F) return qwb_fail(QWB_ERR_ARG, "bias_act: rows of %d values hold no %d columns", ld, F);
+    if (act < 0 || act > 3) return qwb_fail(QWB_ERR_ARG, "bias_act: unknown activation %d", act);
+    const size_t n = (size_t)T * F;
+    const int block = 256;
+    const int grid = (int)((n + block - 1) / block < 148 * 16 ? (n + block - 1) / block : 148 * 16);
+    if (out_dtype == QWB_DT_F32) qwb_launch(bias_act_kernel<float>, grid, block, 0, stream, x, ld, bias, (float*)out, n, F, act);
+    else if (out_dtype == QWB_DT_BF16) qwb_launch(bias_act_kernel<bf16>, grid, block, 0, stream, x, ld, bias, (bf16*)out, n, F, act);
+    else return qwb_fail(QWB_ERR_ARG, "bias_act: unknown dtype %d", out_dtype);
+    return qwb_check_launch("bias_act");
+}

@@ -9,9 +9,10 @@
 // ggml-cuda/rope.cu:676-754).
 #include "common.cuh"
 
-// angle[t,i] = pos[t] * inv_freq[i], in double: positions of thousands keep their digits.
+// angle[t,i] = pos[t] * inv_freq[i], in double: positions of thousands keep their digits.  `factor` multiplies
+// cos and sin (1 for a plain rotation; a scaled rotation for long contexts brings its own).
 __global__ void rope_table_kernel(const int* __restrict__ pos, const double* __restrict__ inv_freq,
-                                  float* __restrict__ cos_out, float* __restrict__ sin_out, int T, int half) {
+                                  float* __restrict__ cos_out, float* __restrict__ sin_out, int T, int half, double factor) {
     pdl_wait();
     pdl_launch_dependents();
     const int n = T * half;
@@ -19,18 +20,18 @@ __global__ void rope_table_kernel(const int* __restrict__ pos, const double* __r
         const int t = i / half, j = i - t * half;
         double s, c;
         sincos((double)pos[t] * inv_freq[j], &s, &c);
-        cos_out[i] = (float)c;
-        sin_out[i] = (float)s;
+        cos_out[i] = (float)(c * factor);
+        sin_out[i] = (float)(s * factor);
     }
 }
 
 extern "C" int qwb_rope_table(const int* pos, const double* inv_freq, float* cos_out, float* sin_out,
-                              int T, int half, cudaStream_t stream) {
+                              int T, int half, double factor, cudaStream_t stream) {
     if (T <= 0 || half <= 0) return 0;
     const int n = T * half, block = 128;
     int grid = (n + block - 1) / block;
     if (grid > 148 * 8) grid = 148 * 8;
-    qwb_launch(rope_table_kernel, grid, block, 0, stream, pos, inv_freq, cos_out, sin_out, T, half);
+    qwb_launch(rope_table_kernel, grid, block, 0, stream, pos, inv_freq, cos_out, sin_out, T, half, factor);
     return qwb_check_launch("rope_table");
 }
 

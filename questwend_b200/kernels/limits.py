@@ -11,3 +11,37 @@ def head_dim_refusal(head_dim: int) -> str | None:
         return (f"the attention kernels take head sizes that are multiples of {HEAD_DIM_STEP} from {HEAD_DIM_STEP} to "
                 f"{MAX_HEAD_DIM}, not {head_dim}")
     return None
+
+
+CONV_MAX_TAPS = 8           # csrc/recurrent.cu: QWB_CONV_MAX_TAPS
+SCAN_MAX_THREADS = 1024     # a recurrent state's columns x ceil(rows / 64) threads of one block
+LATENT_MAX_RANK = 512       # csrc/attention_latent.cu: QWB_LATENT_MAX_L
+LATENT_MAX_ROW = 1024       # ... QWB_LATENT_MAX_ROW
+MOE_MAX_TOP = 16            # csrc/moe.cu: QWB_MOE_MAX_TOP
+
+
+def conv_taps_refusal(taps: int) -> str | None:
+    if not 1 <= taps <= CONV_MAX_TAPS:
+        return f"the short convolution takes 1 to {CONV_MAX_TAPS} taps, not {taps}"
+    return None
+
+
+def state_matrix_refusal(rows: int, cols: int) -> str | None:
+    """A recurrent state of rows x cols per head (state or key size x value size)."""
+    if rows <= 0 or cols <= 0 or cols * -(-rows // 64) > SCAN_MAX_THREADS:
+        return (f"the recurrence kernels keep a state of up to value size x ceil(key or state size / 64) <= "
+                f"{SCAN_MAX_THREADS} per head, not {rows} x {cols}")
+    return None
+
+
+def latent_refusal(rank: int, rot_dim: int) -> str | None:
+    if rank <= 0 or rot_dim < 0 or rank > LATENT_MAX_RANK or rank + rot_dim > LATENT_MAX_ROW:
+        return (f"the latent attention kernel takes a latent of up to {LATENT_MAX_RANK} values and a cached row of up to "
+                f"{LATENT_MAX_ROW}, not {rank} + {rot_dim}")
+    return None
+
+
+def moe_refusal(experts: int, top: int) -> str | None:
+    if experts <= 0 or not 1 <= top <= min(experts, MOE_MAX_TOP):
+        return f"the router chooses 1 to {MOE_MAX_TOP} of its experts, not {top} of {experts}"
+    return None

@@ -162,15 +162,65 @@ def add_inplace(out: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def rmsnorm_onto(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
+                 cast_dtype: torch.dtype | None = None) -> torch.Tensor | None:
+    """h += y / rms(y) * weight, row by row, in 32-bit and in place: the norm on a sublayer's output.  With
+    ``cast_dtype`` the new h is also returned in that dtype (for the next product); float32 returns h itself."""
+    _need(h, "h", torch.float32, 2)
+    _need(y, "y", torch.float32, 2)
+    _need(weight, "weight", torch.float32, 1)
+    T, D = h.shape
+    if y.shape != h.shape or weight.numel() != D:
+        raise KernelError(f"rmsnorm_onto: h {tuple(h.shape)}, y {tuple(y.shape)}, weight of {weight.numel()}")
+    cast = None
+    if cast_dtype is not None and cast_dtype != torch.float32:
+        cast = torch.empty((T, D), dtype=cast_dtype, device=h.device)
+    _call("elementwise", "qwb_rmsnorm_onto", _ptr(y), _ptr(weight), _ptr(h), _ptr(cast),
+          _i(_dt(cast_dtype) if cast is not None else DT_F32), _i(T), _i(D), _f(eps), _stream())
+    if cast_dtype is None:
+        return None
+    return h if cast is None else cast
+
+
+ACTIVATIONS = {"none": 0, "relu2": 1, "gelu_tanh": 2, "silu": 3}
+
+
+def bias_act(x: torch.Tensor, bias: torch.Tensor | None, activation: str, out_dtype: torch.dtype,
+             col0: int = 0, n_cols: int | None = None) -> torch.Tensor:
+    """act(x + bias) for float32 x [T, F], or for its columns ``col0 .. col0 + n_cols``; ``activation`` one of
+    ``ACTIVATIONS``.  Returns [T, F] (or [T, n_cols]) in ``out_dtype``; a float32 result of whole rows replaces x.
+    With no bias and no activation this is the cast of a (slice of a) 32-bit result to a product's operand dtype."""
+    _need(x, "x", torch.float32, 2)
+    T, ld = x.shape
+    F = ld - col0 if n_cols is None else n_cols
+    if col0 < 0 or F <= 0 or col0 + F > ld:
+        raise KernelError(f"bias_act: columns {col0}..{col0 + F} of rows of {ld}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.numel() != F:
+            raise KernelError(f"bias_act: bias of {bias.numel()} for rows of {F}")
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"bias_act: unknown activation '{activation}'")
+    whole = F == ld
+    if whole and out_dtype == torch.float32 and bias is None and activation == "none":
+        return x
+    out = x if (out_dtype == torch.float32 and whole) else torch.empty((T, F), dtype=out_dtype, device=x.device)
+    _call("elementwise", "qwb_bias_act", ctypes.c_void_p(x.data_ptr() + 4 * col0), _i(ld), _ptr(bias), _ptr(out),
+          _i(_dt(out_dtype)), _i(T), _i(F), _i(ACTIVATIONS[activation]), _stream())
+    return out
+
+
 # ----------------------------------------------------------------------------- rope + cache write
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-    """cos and sin of positions[t] * inv_freq[i] as float32 [T, half]; the angles are formed in float64."""
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, factor: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos and sin of positions[t] * inv_freq[i], times ``factor``, as float32 [T, half]; the angles are formed in
+    float64."""
     _need(positions, "positions", torch.int32, 1)
     _need(inv_freq, "inv_freq", torch.float64, 1)
     T, half = positions.numel(), inv_freq.numel()
     cos = torch.empty((T, half), dtype=torch.float32, device=positions.device)
     sin = torch.empty_like(cos)
-    _call("rope_kv", "qwb_rope_table", _ptr(positions), _ptr(inv_freq), _ptr(cos), _ptr(sin), _i(T), _i(half), _stream())
+    _call("rope_kv", "qwb_rope_table", _ptr(positions), _ptr(inv_freq), _ptr(cos), _ptr(sin), _i(T), _i(half),
+          ctypes.c_double(factor), _stream())
     return cos, sin
 
 
@@ -615,6 +665,216 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store", out:
         tile_n = 128 if epilogue == "swiglu" else (128 if N >= 1024 else 64)
     _call("gemm_tc", "qwb_gemm_tc", _ptr(x), _ptr(weight), _ptr(out), _i(TC_EPILOGUES[epilogue]), _i(M), _i(N), _i(K),
           _i(tile_n), _ptr(gemm_tc_error_word(x.device)), _stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- recurrent mixers
+CONV_MAX_TAPS = 8
+
+
+def short_conv(x: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: torch.Tensor | None,
+               tail: torch.Tensor, ctx, activation: bool = True, update_tail: bool = True) -> torch.Tensor:
+    """Causal convolution over time, per channel, of columns ``col0 .. col0 + channels`` of float32 ``x`` [T, ld], with
+    SiLU after it (``activation``).  ``weight`` [channels, taps]: the last tap is the current token's.  ``tail``
+    [slots, taps - 1, channels] float32 holds each sequence's last inputs (zero for a new one) and is brought up to
+    date (``update_tail``).  ``ctx``: the step (tok_seq, cu_seqlens, slots).  Returns float32 [T, channels]."""
+    _need(x, "x", torch.float32, 2)
+    _need(weight, "weight", torch.float32, 2)
+    _need(tail, "tail", torch.float32, 3)
+    T, ld = x.shape
+    taps = weight.shape[1]
+    if weight.shape[0] != channels or col0 < 0 or col0 + channels > ld:
+        raise KernelError(f"short_conv: weight {tuple(weight.shape)} for columns {col0}..{col0 + channels} of {ld}")
+    if tuple(tail.shape[1:]) != (taps - 1, channels):
+        raise KernelError(f"short_conv: tail {tuple(tail.shape)} does not fit {taps} taps of {channels} channels")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+    out = torch.empty((T, channels), dtype=torch.float32, device=x.device)
+    _call("recurrent", "qwb_short_conv", ctypes.c_void_p(x.data_ptr() + 4 * col0), _i(ld), _ptr(weight), _ptr(bias),
+          _ptr(tail), _ptr(ctx.tok_seq), _ptr(ctx.cu_seqlens), _ptr(ctx.slots), _ptr(out), _i(T), _i(ctx.n_seqs),
+          _i(channels), _i(taps), _i(1 if activation else 0), _i(1 if update_tail else 0), _stream(),
+          kernels=2 if (update_tail and taps > 1) else 1)
+    return out
+
+
+def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_col0: int, dt_bias, a_log, d_skip, state: torch.Tensor, ctx,
+             heads: int, vdim: int, n_state: int, groups: int, write_state: bool = True) -> torch.Tensor:
+    """The Mamba-2 recurrence over a step's tokens.  ``xbc`` float32 [T, heads * vdim + 2 * groups * n_state] (x | B | C,
+    after convolution and SiLU); the raw step sizes are columns ``dt_col0 ..`` of float32 ``dt`` [T, ld]; ``state``
+    float32 [slots, heads, n_state, vdim] is read and written back.  Returns y float32 [T, heads * vdim]."""
+    _need(xbc, "xbc", torch.float32, 2)
+    _need(dt, "dt", torch.float32, 2)
+    _need(state, "state", torch.float32, 4)
+    T = xbc.shape[0]
+    if xbc.shape[1] != heads * vdim + 2 * groups * n_state or tuple(state.shape[1:]) != (heads, n_state, vdim):
+        raise KernelError(f"ssm_scan: xbc {tuple(xbc.shape)}, state {tuple(state.shape)} do not fit {heads} heads of "
+                          f"{vdim}, state {n_state}, {groups} groups")
+    for name, t in (("dt_bias", dt_bias), ("A_log", a_log), ("D", d_skip)):
+        _need(t, name, torch.float32, 1)
+        if t.numel() != heads:
+            raise KernelError(f"ssm_scan: {name} has {t.numel()} entries for {heads} heads")
+    y = torch.empty((T, heads * vdim), dtype=torch.float32, device=xbc.device)
+    _call("recurrent", "qwb_ssm_scan", _ptr(xbc), _i(xbc.shape[1]), ctypes.c_void_p(dt.data_ptr() + 4 * dt_col0),
+          _i(dt.shape[1]), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), _ptr(ctx.cu_seqlens), _ptr(ctx.slots),
+          _ptr(y), _i(ctx.n_seqs), _i(heads), _i(vdim), _i(n_state), _i(groups), _i(1 if write_state else 0), _stream())
+    return y
+
+
+def delta_rule(qkv: torch.Tensor, b_raw: torch.Tensor, b_col0: int, a_raw: torch.Tensor, dt_bias, a_log,
+               state: torch.Tensor, ctx, heads: int, key_heads: int, key_dim: int, vdim: int, unit_eps: float,
+               q_scale: float, write_state: bool = True) -> torch.Tensor:
+    """The gated delta rule with a decay per head and key channel, over a step's tokens.  ``qkv`` float32
+    [T, 2 * key_heads * key_dim + heads * vdim] (q | k | v after convolution and SiLU; q and k are made unit vectors
+    in place, q times ``q_scale``); columns ``b_col0 .. b_col0 + heads`` of ``b_raw`` [T, ld] and ``a_raw``
+    [T, heads * key_dim] are the raw write strengths and decays; ``state`` float32 [slots, heads, key_dim, vdim].  Returns o float32 [T, heads * vdim]."""
+    _need(qkv, "qkv", torch.float32, 2)
+    _need(b_raw, "b_raw", torch.float32, 2)
+    _need(a_raw, "a_raw", torch.float32, 2)
+    _need(state, "state", torch.float32, 4)
+    _need(dt_bias, "dt_bias", torch.float32, 1)
+    _need(a_log, "A_log", torch.float32, 1)
+    T = qkv.shape[0]
+    if (qkv.shape[1] != 2 * key_heads * key_dim + heads * vdim or b_raw.shape[0] != T or b_col0 + heads > b_raw.shape[1]
+            or tuple(a_raw.shape) != (T, heads * key_dim) or tuple(state.shape[1:]) != (heads, key_dim, vdim)
+            or dt_bias.numel() != heads * key_dim or a_log.numel() != heads):
+        raise KernelError(f"delta_rule: qkv {tuple(qkv.shape)}, b {tuple(b_raw.shape)}, a {tuple(a_raw.shape)}, state "
+                          f"{tuple(state.shape)} do not fit {heads} heads ({key_heads} key heads) of {key_dim} x {vdim}")
+    dev = qkv.device
+    kq = torch.empty((T, key_heads), dtype=torch.float32, device=dev)
+    beta = torch.empty((T, heads), dtype=torch.float32, device=dev)
+    decay = torch.empty((T, heads * key_dim), dtype=torch.float32, device=dev)
+    _call("recurrent", "qwb_delta_prep", _ptr(qkv), _i(qkv.shape[1]), _ptr(kq), ctypes.c_void_p(b_raw.data_ptr() + 4 * b_col0),
+          _i(b_raw.shape[1]), _ptr(beta), _ptr(a_raw),
+          _ptr(dt_bias), _ptr(a_log), _ptr(decay), _i(T), _i(heads), _i(key_heads), _i(key_dim), _f(unit_eps), _f(q_scale),
+          _stream())
+    o = torch.empty((T, heads * vdim), dtype=torch.float32, device=dev)
+    _call("recurrent", "qwb_delta_scan", _ptr(qkv), _i(qkv.shape[1]), _ptr(kq), _ptr(beta), _ptr(decay), _ptr(state),
+          _ptr(ctx.cu_seqlens), _ptr(ctx.slots), _ptr(o), _i(ctx.n_seqs), _i(heads), _i(key_heads), _i(key_dim), _i(vdim),
+          _i(1 if write_state else 0), _stream())
+    return o
+
+
+def gated_part_norm(y: torch.Tensor, gate: torch.Tensor, gate_col0: int, weight: torch.Tensor, n_parts: int, eps: float,
+                    gate_first: bool, out_dtype: torch.dtype) -> torch.Tensor:
+    """RMS norm over ``n_parts`` equal parts of every row of float32 ``y`` [T, D], with a gate from columns
+    ``gate_col0 ..`` of float32 ``gate`` [T, ld].  ``gate_first``: y * silu(gate) is normed, times the weight; else y is
+    normed, times the weight, times sigmoid(gate).  ``weight`` has D entries, or D / n_parts shared by all parts."""
+    _need(y, "y", torch.float32, 2)
+    _need(gate, "gate", torch.float32, 2)
+    _need(weight, "weight", torch.float32, 1)
+    T, D = y.shape
+    if D % n_parts or weight.numel() not in (D, D // n_parts) or gate_col0 + D > gate.shape[1] or gate.shape[0] != T:
+        raise KernelError(f"gated_part_norm: y {tuple(y.shape)} in {n_parts} parts, weight of {weight.numel()}, gate "
+                          f"{tuple(gate.shape)} from column {gate_col0}")
+    out = torch.empty((T, D), dtype=out_dtype, device=y.device)
+    _call("recurrent", "qwb_gated_part_norm", _ptr(y), ctypes.c_void_p(gate.data_ptr() + 4 * gate_col0), _i(gate.shape[1]),
+          _ptr(weight), _i(weight.numel()), _ptr(out), _i(_dt(out_dtype)), _i(T), _i(n_parts), _i(D // n_parts), _f(eps),
+          _i(0 if gate_first else 1), _stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- latent attention
+LATENT_MAX_RANK = 512       # csrc/attention_latent.cu: QWB_LATENT_MAX_L
+LATENT_MAX_ROW = 1024       # ... QWB_LATENT_MAX_ROW: latent + rotated key part
+
+
+def latent_prep(q: torch.Tensor, dkv: torch.Tensor, c_weight: torch.Tensor, cos, sin, ctx, page_table, pool,
+                heads: int, dim: int, rot_dim: int, rank: int, eps: float, store: bool = True):
+    """Per token: the latent (``dkv[:, :rank]``, RMS-normed, times ``c_weight``) and the rotated shared key part
+    (``dkv[:, rank:]``, pairs (2i, 2i + 1) turned by cos/sin [T, half]) go into the cache row of the token's position;
+    each head's rotated query part is turned the same way.  ``q`` float32 [T, heads * (dim + rot_dim)].
+    Returns (q_plain [heads, T, dim] in the pool's dtype, q_rot float32 [T, heads, rot_dim])."""
+    _need(q, "q", torch.float32, 2)
+    _need(dkv, "dkv", torch.float32, 2)
+    _need(c_weight, "c_weight", torch.float32, 1)
+    _need(pool, "pool", ndim=4)
+    _need(page_table, "page_table", torch.int32, 2)
+    T = q.shape[0]
+    half = 0
+    if cos is not None:
+        _need(cos, "cos", torch.float32, 2)
+        _need(sin, "sin", torch.float32, 2)
+        half = cos.shape[1]
+        if cos.shape[0] != T or sin.shape != cos.shape or 2 * half > rot_dim:
+            raise KernelError(f"latent_prep: cos/sin {tuple(cos.shape)} do not fit {T} tokens and {rot_dim} rotated values")
+    if (q.shape[1] != heads * (dim + rot_dim) or tuple(dkv.shape) != (T, rank + rot_dim) or c_weight.numel() != rank
+            or pool.shape[1] != 1 or pool.shape[3] != rank + rot_dim):
+        raise KernelError(f"latent_prep: q {tuple(q.shape)}, dkv {tuple(dkv.shape)}, pool {tuple(pool.shape)} do not fit "
+                          f"{heads} heads of {dim} + {rot_dim}, latent {rank}")
+    q_plain = torch.empty((heads, T, dim), dtype=pool.dtype, device=q.device)
+    q_rot = torch.empty((T, heads, rot_dim), dtype=torch.float32, device=q.device)
+    _call("attention_latent", "qwb_latent_prep", _ptr(q), _ptr(dkv), _ptr(c_weight), _ptr(cos), _ptr(sin), _ptr(ctx.tok_seq),
+          _ptr(ctx.tok_pos), _ptr(page_table), _ptr(pool), _i(_dt(pool.dtype)), _ptr(q_plain), _ptr(q_rot), _i(T), _i(heads),
+          _i(dim), _i(rot_dim), _i(rank), _i(half), _f(eps), _i(pool.shape[2]), _i(page_table.shape[1]),
+          _i(1 if store else 0), _stream())
+    return q_plain, q_rot
+
+
+def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, pool: torch.Tensor, page_table, ctx, sink, scale: float,
+                     window: int = 0) -> torch.Tensor:
+    """Attention of every head over the shared cached rows [latent | rotated key part]; the values are the latents.
+    ``q_abs`` float32 [heads, T, rank] (the queries taken into the latent space), ``q_rot`` float32 [T, heads, rot_dim];
+    ``sink`` float32 [heads] or None: one more term exp(sink) in the softmax's denominator.  Causal; ``window`` > 0:
+    a position sees itself and the window - 1 before it.  Returns [heads, T, rank] in the pool's dtype."""
+    _need(q_abs, "q_abs", torch.float32, 3)
+    _need(q_rot, "q_rot", torch.float32, 3)
+    _need(pool, "pool", ndim=4)
+    _need(page_table, "page_table", torch.int32, 2)
+    H, T, L = q_abs.shape
+    R = q_rot.shape[2]
+    if tuple(q_rot.shape[:2]) != (T, H) or pool.shape[1] != 1 or pool.shape[3] != L + R:
+        raise KernelError(f"latent_attention: q_abs {tuple(q_abs.shape)}, q_rot {tuple(q_rot.shape)}, pool {tuple(pool.shape)}")
+    if sink is not None:
+        _need(sink, "sink", torch.float32, 1)
+        if sink.numel() != H:
+            raise KernelError(f"latent_attention: {sink.numel()} sinks for {H} heads")
+    out = torch.empty((H, T, L), dtype=pool.dtype, device=q_abs.device)
+    _call("attention_latent", "qwb_latent_attn", _ptr(q_abs), _ptr(q_rot), _ptr(pool), _ptr(page_table), _ptr(ctx.cu_seqlens),
+          _ptr(ctx.pos0), _ptr(sink), _ptr(out), _i(_dt(pool.dtype)), _i(ctx.n_seqs), _i(T), _i(ctx.max_new), _i(H), _i(L),
+          _i(R), _i(pool.shape[2]), _i(page_table.shape[1]), _f(scale), _i(window), _stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- routed experts
+MOE_MAX_TOP = 16            # csrc/moe.cu: QWB_MOE_MAX_TOP
+_MOE_SLOTS_PER_LAUNCH = 65535
+
+
+def moe_route(logits: torch.Tensor, top: int, renormalize: bool = False):
+    """softmax over float32 ``logits`` [T, E]; the ``top`` largest per row (ties to the lower index).  Returns
+    (chosen int32 [T, top], weight float32 [T, top]): the chosen scores, divided by their sum if ``renormalize``."""
+    _need(logits, "logits", torch.float32, 2)
+    T, E = logits.shape
+    chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weight = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    _call("moe", "qwb_moe_route", _ptr(logits), _ptr(chosen), _ptr(weight), _i(T), _i(E), _i(top),
+          _i(1 if renormalize else 0), _stream())
+    return chosen, weight
+
+
+def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor,
+                weight: torch.Tensor) -> torch.Tensor:
+    """sum_k weight[t, k] * down_e(silu(gate_e x_t) * up_e x_t), e = chosen[t, k].  ``x`` [T, D] and the stacked
+    weights (``w_gate_up`` [E, 2F, D]: gate rows, then up rows; ``w_down`` [E, D, F]) in one dtype.  Returns float32 [T, D]."""
+    _need(x, "x", w_gate_up.dtype, 2)
+    _need(w_gate_up, "w_gate_up", ndim=3)
+    _need(w_down, "w_down", w_gate_up.dtype, 3)
+    _need(chosen, "chosen", torch.int32, 2)
+    _need(weight, "weight", torch.float32, 2)
+    T, D = x.shape
+    E, F2, _ = w_gate_up.shape
+    F, top = F2 // 2, chosen.shape[1]
+    if w_gate_up.shape[2] != D or tuple(w_down.shape) != (E, D, F) or tuple(chosen.shape) != (T, top) or weight.shape != chosen.shape:
+        raise KernelError(f"moe_experts: x {tuple(x.shape)}, gate/up {tuple(w_gate_up.shape)}, down {tuple(w_down.shape)}, "
+                          f"chosen {tuple(chosen.shape)}")
+    act = torch.empty((T * top, F), dtype=x.dtype, device=x.device)
+    out = torch.empty((T, D), dtype=torch.float32, device=x.device)
+    per = max(1, _MOE_SLOTS_PER_LAUNCH // top)
+    for t0 in range(0, T, per):
+        n = min(per, T - t0)
+        _call("moe", "qwb_moe_experts", _ptr(x[t0:t0 + n]), _ptr(w_gate_up), _ptr(w_down), _ptr(chosen[t0:t0 + n]),
+              _ptr(weight[t0:t0 + n]), _ptr(act[t0 * top:(t0 + n) * top]), _ptr(out[t0:t0 + n]), _i(_dt(x.dtype)), _i(n),
+              _i(D), _i(F), _i(top), _stream(), kernels=2)
     return out
 
 

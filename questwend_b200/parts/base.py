@@ -39,11 +39,14 @@ class KVSpec:
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    values: bool = True         # False: one row per token and no separate values (a latent that is key and value at once);
+                                # the unit's ``v_pool`` is then None
 
 
 @dataclass(frozen=True)
 class StateSpec:
-    """Per-sequence state of fixed size (a recurrent state, a convolution tail)."""
+    """Per-sequence state of fixed size (a recurrent state, a convolution tail).  A mixer that keeps several
+    (``state_spec`` returns a tuple of these) finds them as a tuple in ``UnitCache.state``, in the same order."""
     shape: tuple
     dtype: torch.dtype = torch.float32
 
@@ -85,7 +88,7 @@ class UnitCache:
         self.group_id = group_id
         self.k_pool = k_pool        # [n_pages, Hkv, page_size, hd] or None
         self.v_pool = v_pool
-        self.state = state          # [n_slots, *shape] or None
+        self.state = state          # [n_slots, *shape], a tuple of such (one per StateSpec), or None
         self.writable = writable
 
 
@@ -144,6 +147,10 @@ class Norm(Part):
     def forward(self, x, delta=None, write_sum=False, rows=None, out_dtype=None) -> torch.Tensor:
         raise NotImplementedError
 
+    def add_normed(self, h, y, cast_dtype=None):
+        """h += norm(y), in place (the norm on a sublayer's output); returns the new h in ``cast_dtype`` if one is given."""
+        raise NotImplementedError
+
 
 class PositionEncoding(Part):
     """Gives a mixer what it needs to encode positions (for a rotation: cos and sin of
@@ -160,7 +167,7 @@ class Mixer(Part):
     def kv_spec(self) -> KVSpec | None:
         return None
 
-    def state_spec(self) -> StateSpec | None:
+    def state_spec(self) -> StateSpec | tuple | None:
         return None
 
     adds_to_residual = False    # True: forward(..., residual=h) adds its output onto h in place and returns None, or

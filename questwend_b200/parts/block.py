@@ -54,4 +54,58 @@ class PreNormBlock(Block):
         return h, delta
 
 
+class OutputNormBlock(Block):
+    """h += norm1(mixer(h)); h += norm2(feed_forward(h)): the sublayers read the stream itself and the norms sit on
+    their outputs.  The stream and both sums are 32-bit; the norm kernel that adds onto the stream also hands back the
+    stream in the dtype of the next product's operands, and the block leaves it in ``ctx.shared`` for the block after it.
+    A layer without a feed-forward (``feed_forward`` None) has the first half only.
+    params: mixer_norm, ffn_norm (the norms' tensor names after the layer's prefix), mixer_prefix, ffn_prefix."""
+
+    def __init__(self, spec, runtime, layer=None, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        px = spec.prefix
+
+        def norm(name):
+            return build_part("norm", replace(layer.norm, prefix=px, params={**dict(layer.norm.params), "name": name}), runtime)
+
+        self.norm1 = norm(p.get("mixer_norm", "norm1"))
+        self.mixer = build_part("mixer", replace(layer.mixer, prefix=px + p.get("mixer_prefix", "mix") + "."),
+                                runtime, position=position)
+        self.ffn = self.norm2 = None
+        if layer.feed_forward is not None:
+            self.norm2 = norm(p.get("ffn_norm", "norm2"))
+            self.ffn = build_part("feed_forward", replace(layer.feed_forward, prefix=px + p.get("ffn_prefix", "mlp") + "."), runtime)
+
+    def parts(self):
+        return [part for part in (self.norm1, self.mixer, self.norm2, self.ffn) if part is not None]
+
+    def tensors(self):
+        return [t for part in self.parts() for t in part.tensors()]
+
+    def bind(self, weights):
+        for part in self.parts():
+            part.bind(weights)
+
+    def kernel_modules(self):
+        return ("elementwise", *(m for part in self.parts() for m in part.kernel_modules()))
+
+    def forward(self, h, delta, ctx, cache):
+        from ..kernels import ops
+        dtype = self.runtime.dtype
+        if delta is not None:                                   # a block of another arrangement came before
+            if isinstance(delta, ops.SplitSum):
+                delta.add_onto(h)
+            else:
+                ops.add_inplace(h, delta)
+        have = ctx.shared.get("stream_as_operand")
+        x = have[1] if have is not None and have[0] is h else ops.bias_act(h, None, "none", dtype)
+        x = self.norm1.add_normed(h, self.mixer.forward(x, ctx, cache), cast_dtype=dtype)
+        if self.ffn is not None:
+            x = self.norm2.add_normed(h, self.ffn.forward(x, ctx), cast_dtype=dtype)
+        ctx.shared["stream_as_operand"] = (h, x)
+        return h, None
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("output_norm", OutputNormBlock)

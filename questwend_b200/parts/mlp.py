@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from ..weights.manifest import MATRIX, TensorSpec
+from ..weights.manifest import MATRIX, VECTOR, TensorSpec
 from .base import FeedForward, take_weight
 from .linear import kernel_modules as linear_modules, linear, linear_onto, linear_swiglu
 from .registry import register_feed_forward
@@ -54,4 +54,40 @@ class GatedMLP(FeedForward):
         return linear(act, self.w_down)
 
 
+class BiasedMLP(FeedForward):
+    """Ungated: down( act(up(x) + b_up) ) + b_down.
+    params: hidden_size, intermediate_size, activation (one of ``ops.ACTIVATIONS``), names (optional overrides)."""
+
+    NAMES = {"up": "up", "up_bias": "up.b", "down": "down", "down_bias": "down.b"}
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.hidden = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.activation = str(spec.params["activation"])
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"feed-forward '{self.prefix}': unknown activation '{self.activation}'; known: "
+                             f"{', '.join(ops.ACTIVATIONS)}")
+        self.names = {**self.NAMES, **dict(spec.params.get("names", {}))}
+
+    def tensors(self):
+        n, px = self.names, self.prefix
+        return [TensorSpec(px + n["up"], (self.inter, self.hidden), MATRIX), TensorSpec(px + n["up_bias"], (self.inter,), VECTOR),
+                TensorSpec(px + n["down"], (self.hidden, self.inter), MATRIX), TensorSpec(px + n["down_bias"], (self.hidden,), VECTOR)]
+
+    def bind(self, weights):
+        n, px = self.names, self.prefix
+        self.w_up, self.w_down = weights[px + n["up"]], weights[px + n["down"]]
+        self.b_up = weights[px + n["up_bias"]].to(torch.float32).contiguous()
+        self.b_down = weights[px + n["down_bias"]].to(torch.float32).contiguous()
+
+    def kernel_modules(self):
+        return ("elementwise", *linear_modules(self.runtime.dtype))
+
+    def forward(self, x, ctx):
+        act = ops.bias_act(linear(x, self.w_up), self.b_up, self.activation, self.runtime.dtype)
+        return ops.bias_act(linear(act, self.w_down), self.b_down, "none", torch.float32)
+
+
 register_feed_forward("gated_mlp", GatedMLP)
+register_feed_forward("biased_mlp", BiasedMLP)

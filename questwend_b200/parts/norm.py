@@ -11,19 +11,20 @@ from .registry import register_norm
 
 
 class RMSNorm(Norm):
-    """params: dim, eps; tensor: <prefix>weight [dim]."""
+    """params: dim, eps, name (default "weight"); tensor: <prefix><name> [dim]."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.dim = int(spec.params["dim"])
         self.eps = float(spec.params["eps"])
+        self.name = self.prefix + str(spec.params.get("name", "weight"))
         self.weight = None
 
     def tensors(self):
-        return [TensorSpec(self.prefix + "weight", (self.dim,), VECTOR, NORM_WEIGHT)]
+        return [TensorSpec(self.name, (self.dim,), VECTOR, NORM_WEIGHT)]
 
     def bind(self, weights):
-        self.weight = weights[self.prefix + "weight"].to(torch.float32).contiguous()
+        self.weight = weights[self.name].to(torch.float32).contiguous()
 
     def kernel_modules(self):
         return ("elementwise",)
@@ -33,6 +34,10 @@ class RMSNorm(Norm):
     def forward(self, x, delta=None, write_sum=False, rows=None, out_dtype=None):
         return ops.rmsnorm(x, self.weight, self.eps, out_dtype or self.runtime.dtype, delta=delta,
                            write_sum=write_sum, rows=rows)
+
+    def add_normed(self, h, y, cast_dtype=None):
+        """h += y / rms(y) * w in place (32-bit); the new h in ``cast_dtype`` if one is given."""
+        return ops.rmsnorm_onto(h, y, self.weight, self.eps, cast_dtype)
 
 
 register_norm("rms", RMSNorm)

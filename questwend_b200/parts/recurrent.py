@@ -1,0 +1,167 @@
+"""Mixers that carry a state of fixed size from token to token instead of keys and values: the state-space
+recurrence of Mamba-2 and the gated delta rule with a decay per key channel.  Both keep, per sequence, a 32-bit
+state matrix per head and the last inputs of a short causal convolution, in the cache's per-slot state rows; a
+prompt and a single token run through the same kernels (``csrc/recurrent.cu``).  The projections are matrix
+products in the engine's dtype with 32-bit results; everything between them is 32-bit.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..kernels.limits import conv_taps_refusal, state_matrix_refusal
+from ..weights.manifest import MATRIX, NORM_WEIGHT, VECTOR, TensorSpec
+from .base import Mixer, StateSpec, take_weight
+from .linear import kernel_modules as linear_modules, linear
+from .registry import register_mixer
+
+
+def _f32(weights, name):
+    return weights[name].to(torch.float32).contiguous()
+
+
+class Mamba2Mixer(Mixer):
+    """Mamba-2.  One projection gives z | x | B | C | dt; x, B and C pass a causal convolution (with bias) and SiLU;
+    per head h (group h // (heads / groups)):  dt = softplus(dt + dt_bias_h);  S = exp(-exp(A_log_h) dt) S + dt B x^T;
+    y = S^T C + D_h x;  then y * silu(z), an RMS norm over ``norm_groups`` equal parts of the row, times the norm's
+    weight, and the output projection.
+
+    params: hidden_size, heads, vdim, state, groups, norm_groups, conv (taps), norm_eps, names (optional overrides).
+    State per sequence: the convolution's last taps - 1 inputs [taps - 1, channels] and S [heads, state, vdim]."""
+
+    NAMES = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "dt_bias": "dt_bias", "A_log": "A_log", "D": "D",
+             "norm": "norm", "out": "o"}
+
+    def __init__(self, spec, runtime, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.heads, self.vdim, self.n_state = int(p["heads"]), int(p["vdim"]), int(p["state"])
+        self.groups, self.norm_groups, self.taps = int(p["groups"]), int(p["norm_groups"]), int(p["conv"])
+        self.eps = float(p["norm_eps"])
+        self.names = {**self.NAMES, **dict(p.get("names", {}))}
+        self.inner = self.heads * self.vdim
+        self.channels = self.inner + 2 * self.groups * self.n_state
+        if self.heads % self.groups:
+            raise ValueError(f"mamba2 '{self.prefix}': {self.heads} heads are not a multiple of {self.groups} groups")
+        if self.inner % self.norm_groups:
+            raise ValueError(f"mamba2 '{self.prefix}': {self.inner} values cannot be normed in {self.norm_groups} equal parts")
+        for refusal in (conv_taps_refusal(self.taps), state_matrix_refusal(self.n_state, self.vdim)):
+            if refusal:
+                raise ValueError(f"mamba2 '{self.prefix}': {refusal}")
+
+    def tensors(self):
+        n, px, H = self.names, self.prefix, self.heads
+        return [TensorSpec(px + n["in"], (2 * self.inner + 2 * self.groups * self.n_state + H, self.hidden), MATRIX),
+                TensorSpec(px + n["conv"], (self.channels, self.taps), VECTOR),
+                TensorSpec(px + n["conv_bias"], (self.channels,), VECTOR),
+                TensorSpec(px + n["dt_bias"], (H,), VECTOR), TensorSpec(px + n["A_log"], (H,), VECTOR),
+                TensorSpec(px + n["D"], (H,), VECTOR, NORM_WEIGHT),
+                TensorSpec(px + n["norm"], (self.inner,), VECTOR, NORM_WEIGHT),
+                TensorSpec(px + n["out"], (self.hidden, self.inner), MATRIX)]
+
+    def bind(self, weights):
+        n, px = self.names, self.prefix
+        self.w_in, self.w_out = weights[px + n["in"]], weights[px + n["out"]]
+        self.conv_w, self.conv_b = _f32(weights, px + n["conv"]), _f32(weights, px + n["conv_bias"])
+        self.dt_bias, self.a_log, self.d_skip = (_f32(weights, px + n[k]) for k in ("dt_bias", "A_log", "D"))
+        self.norm_w = _f32(weights, px + n["norm"])
+
+    def kernel_modules(self):
+        return ("recurrent", *linear_modules(self.runtime.dtype))
+
+    def state_spec(self):
+        return (StateSpec((self.taps - 1, self.channels), torch.float32),
+                StateSpec((self.heads, self.n_state, self.vdim), torch.float32))
+
+    def forward(self, x, ctx, cache):
+        tail, state = cache.state
+        proj = linear(x, self.w_in)                                   # z | x B C | dt, 32-bit
+        xbc = ops.short_conv(proj, self.inner, self.channels, self.conv_w, self.conv_b, tail, ctx,
+                             update_tail=cache.writable)
+        y = ops.ssm_scan(xbc, proj, self.inner + self.channels, self.dt_bias, self.a_log, self.d_skip, state, ctx,
+                         self.heads, self.vdim, self.n_state, self.groups, write_state=cache.writable)
+        g = ops.gated_part_norm(y, proj, 0, self.norm_w, self.norm_groups, self.eps, gate_first=True,
+                                out_dtype=self.runtime.dtype)
+        return linear(g, self.w_out)
+
+
+class GatedDeltaMixer(Mixer):
+    """The gated delta rule with one decay per head and key channel.  q and k (``key_heads`` heads of ``key_dim``) and v
+    (``heads`` heads of ``vdim``) each pass a causal convolution (no bias) and SiLU; q and k become unit vectors per head
+    (x / sqrt(sum x^2 + ``unit_eps``)), q times key_dim^-1/2; beta = sigmoid(W_b h); decay = exp(-exp(A_log_h) *
+    softplus(W_a2 W_a1 h + dt_bias)) per (head, key channel).  Per head (its q/k head is h // (heads / key_heads)):
+    S = decay[:, None] S;  u = beta (v - S^T k);  S = S + k u^T;  o = S^T q.  Each head's o is RMS-normed over vdim,
+    times a weight shared by the heads, times sigmoid(W_g2 W_g1 h); then the output projection.
+
+    params: hidden_size, heads, key_heads, key_dim, vdim, conv (taps), decay_rank, gate_rank, norm_eps, unit_eps
+    (default 1e-6), names.  State per sequence: the convolutions' last taps - 1 inputs and S [heads, key_dim, vdim]."""
+
+    NAMES = {"q": "q", "k": "k", "v": "v", "q_conv": "q.conv", "k_conv": "k.conv", "v_conv": "v.conv", "beta": "b",
+             "A_log": "A_log", "decay_down": "a1", "decay_up": "a2", "dt_bias": "dt_bias", "gate_down": "g1",
+             "gate_up": "g2", "norm": "norm", "out": "o"}
+
+    def __init__(self, spec, runtime, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.heads, self.key_heads = int(p["heads"]), int(p["key_heads"])
+        self.key_dim, self.vdim, self.taps = int(p["key_dim"]), int(p["vdim"]), int(p["conv"])
+        self.decay_rank, self.gate_rank = int(p["decay_rank"]), int(p["gate_rank"])
+        self.eps, self.unit_eps = float(p["norm_eps"]), float(p.get("unit_eps", 1e-6))
+        self.names = {**self.NAMES, **dict(p.get("names", {}))}
+        if self.heads % self.key_heads:
+            raise ValueError(f"gated delta rule '{self.prefix}': {self.heads} heads are not a multiple of "
+                             f"{self.key_heads} query/key heads")
+        for refusal in (conv_taps_refusal(self.taps), state_matrix_refusal(self.key_dim, self.vdim)):
+            if refusal:
+                raise ValueError(f"gated delta rule '{self.prefix}': {refusal}")
+        self.n_qk = self.key_heads * self.key_dim
+        self.channels = 2 * self.n_qk + self.heads * self.vdim
+
+    def tensors(self):
+        n, px, D, H = self.names, self.prefix, self.hidden, self.heads
+        return [TensorSpec(px + n["q"], (self.n_qk, D), MATRIX), TensorSpec(px + n["q_conv"], (self.n_qk, self.taps), VECTOR),
+                TensorSpec(px + n["k"], (self.n_qk, D), MATRIX), TensorSpec(px + n["k_conv"], (self.n_qk, self.taps), VECTOR),
+                TensorSpec(px + n["v"], (H * self.vdim, D), MATRIX),
+                TensorSpec(px + n["v_conv"], (H * self.vdim, self.taps), VECTOR),
+                TensorSpec(px + n["beta"], (H, D), MATRIX), TensorSpec(px + n["A_log"], (H,), VECTOR),
+                TensorSpec(px + n["norm"], (self.vdim,), VECTOR, NORM_WEIGHT),
+                TensorSpec(px + n["decay_down"], (self.decay_rank, D), MATRIX),
+                TensorSpec(px + n["decay_up"], (H * self.key_dim, self.decay_rank), MATRIX),
+                TensorSpec(px + n["dt_bias"], (H * self.key_dim,), VECTOR),
+                TensorSpec(px + n["gate_down"], (self.gate_rank, D), MATRIX),
+                TensorSpec(px + n["gate_up"], (H * self.vdim, self.gate_rank), MATRIX),
+                TensorSpec(px + n["out"], (D, H * self.vdim), MATRIX)]
+
+    def bind(self, weights):
+        n, px = self.names, self.prefix
+        # one projection for everything that reads the stream: q | k | v | beta | decay latent | gate latent
+        self.w_in = torch.cat([take_weight(weights, px + n[k]) for k in ("q", "k", "v", "beta", "decay_down", "gate_down")],
+                              dim=0).contiguous()
+        self.conv_w = torch.cat([_f32(weights, px + n[k]) for k in ("q_conv", "k_conv", "v_conv")], dim=0).contiguous()
+        self.w_decay_up, self.w_gate_up, self.w_out = (weights[px + n[k]] for k in ("decay_up", "gate_up", "out"))
+        self.a_log, self.dt_bias, self.norm_w = (_f32(weights, px + n[k]) for k in ("A_log", "dt_bias", "norm"))
+
+    def kernel_modules(self):
+        return ("recurrent", "elementwise", *linear_modules(self.runtime.dtype))
+
+    def state_spec(self):
+        return (StateSpec((self.taps - 1, self.channels), torch.float32),
+                StateSpec((self.heads, self.key_dim, self.vdim), torch.float32))
+
+    def forward(self, x, ctx, cache):
+        tail, state = cache.state
+        dtype, C, H = self.runtime.dtype, self.channels, self.heads
+        proj = linear(x, self.w_in)
+        qkv = ops.short_conv(proj, 0, C, self.conv_w, None, tail, ctx, update_tail=cache.writable)
+        a_raw = linear(ops.bias_act(proj, None, "none", dtype, C + H, self.decay_rank), self.w_decay_up)
+        o = ops.delta_rule(qkv, proj, C, a_raw, self.dt_bias, self.a_log, state, ctx, H, self.key_heads, self.key_dim,
+                           self.vdim, self.unit_eps, self.key_dim ** -0.5, write_state=cache.writable)
+        gate = linear(ops.bias_act(proj, None, "none", dtype, C + H + self.decay_rank, self.gate_rank), self.w_gate_up)
+        g = ops.gated_part_norm(o, gate, 0, self.norm_w, H, self.eps, gate_first=False, out_dtype=dtype)
+        return linear(g, self.w_out)
+
+
+register_mixer("mamba2", Mamba2Mixer)
+register_mixer("gated_delta_channelwise", GatedDeltaMixer)

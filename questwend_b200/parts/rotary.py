@@ -33,4 +33,55 @@ class RotaryEncoding(PositionEncoding):
         return ctx.shared[key]
 
 
+def scaled_frequencies(rotary_dim: int, theta: float, factor=None, original=None, fast=None, slow=None):
+    """Angle per position of each pair, in float64, and the factor on cos and sin.  Without ``factor``: theta^(-2i/n), 1.
+    With it (the YaRN form): let d(r) = n ln(original / (2 pi r)) / (2 ln theta), lo = max(floor(d(fast)), 0),
+    hi = min(ceil(d(slow)), n - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1); pair i turns by
+    f_i / factor * ramp_i + f_i * (1 - ramp_i), and cos and sin are multiplied by 0.1 ln(factor) + 1."""
+    import math
+    n = rotary_dim
+    i = torch.arange(n // 2, dtype=torch.float64)
+    f = theta ** (-2.0 * i / n)
+    if factor is None:
+        return f, 1.0
+
+    def pair_of(turns):
+        return n * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(pair_of(fast)), 0)
+    hi = min(math.ceil(pair_of(slow)), n - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+class PairedRotaryEncoding(PositionEncoding):
+    """Rotation of neighbouring pairs (2i, 2i + 1) of the first ``rotary_dim`` values, optionally scaled for long
+    contexts.  params: theta, rotary_dim, and for the scaling (all four or none) factor, original, fast, slow.
+    ``prepare`` gives cos and sin [T, rotary_dim / 2] with the scaling's factor already on them; which values are
+    paired is the business of the kernel that applies them."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.theta = float(p["theta"])
+        self.rotary_dim = int(p["rotary_dim"])
+        if self.rotary_dim <= 0 or self.rotary_dim % 2:
+            raise ValueError(f"rotary size {self.rotary_dim} must be positive and even")
+        scaling = [p.get(k) for k in ("factor", "original", "fast", "slow")]
+        if any(v is None for v in scaling) and not all(v is None for v in scaling):
+            raise ValueError("a scaled rotation needs all of factor, original, fast and slow")
+        freqs, self.factor = scaled_frequencies(self.rotary_dim, self.theta, *[None if v is None else float(v) for v in scaling])
+        self.inv_freq = freqs.to(runtime.device)
+
+    def kernel_modules(self):
+        return ("rope_kv",)
+
+    def prepare(self, ctx):
+        key = ("rotary_pairs", id(self))
+        if key not in ctx.shared:
+            ctx.shared[key] = ops.rope_table(ctx.tok_pos, self.inv_freq, self.factor)
+        return ctx.shared[key]
+
+
 register_position("rotary_neox", RotaryEncoding)
+register_position("rotary_pairs", PairedRotaryEncoding)

@@ -23,7 +23,7 @@ __global__ void short_conv_kernel(const float* __restrict__ x, int ld, const flo
                                   const int* __restrict__ slots, float* __restrict__ out, int T, int C, int taps, int act) {
     pdl_wait();
     pdl_launch_dependents();
-    const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x, t = blockIdx.x;
     if (c >= C || t >= T) return;
     const int b = tok_seq[t];
     const int i = t - cu_seqlens[b];
@@ -60,9 +60,9 @@ extern "C" int qwb_short_conv(const float* x, int ld, const float* w, const floa
     if (T <= 0 || B <= 0) return 0;
     if (C <= 0 || taps < 1 || taps > QWB_CONV_MAX_TAPS || ld < C)
         return qwb_fail(QWB_ERR_ARG, "short_conv: %d channels, %d taps (1 to %d), row stride %d", C, taps, QWB_CONV_MAX_TAPS, ld);
-    if (T > 65535 * 32 || B > 65535) return qwb_fail(QWB_ERR_ARG, "short_conv: %d tokens or %d sequences are too many", T, B);
+    if (B > 65535 || C > 65535 * 128) return qwb_fail(QWB_ERR_ARG, "short_conv: %d sequences or %d channels are too many", B, C);
     const int block = C >= 256 ? 256 : 128;
-    qwb_launch(short_conv_kernel, dim3((C + block - 1) / block, T), block, 0, stream, x, ld, w, bias, (const float*)tail, tok_seq, cu_seqlens, slots, out, T, C, taps, act);
+    qwb_launch(short_conv_kernel, dim3(T, (C + block - 1) / block), block, 0, stream, x, ld, w, bias, (const float*)tail, tok_seq, cu_seqlens, slots, out, T, C, taps, act);
     if (int rc = qwb_check_launch("short_conv")) return rc;
     if (update_tail && taps > 1) {
         qwb_launch(conv_tail_kernel, dim3((C + block - 1) / block, B), block, 0, stream, x, ld, tail, cu_seqlens, slots, B, C, taps);

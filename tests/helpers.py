@@ -60,7 +60,8 @@ def run_trace(model_dir, dtype, steps, max_tokens, out_dir, timeout=600):
     done = [line for line in proc.stdout.splitlines() if line.startswith("done ")]
     assert [d.split()[1] for d in done] == [str(s["step"]) for s in steps], proc.stdout
     with open(os.path.join(model_dir, "config.json")) as f:
-        V = json.load(f)["vocab_size"]
+        cfg = json.load(f)
+        V = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
     out = {}
     for s in steps:
         n = sum(len(e.get("want", [])) for e in s["entries"])

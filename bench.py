@@ -55,6 +55,31 @@ QWEN3_06B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=1024, num_attention
 QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8,
                  intermediate_size=25600)
 MODELS = {"8b": QWEN3_8B, "0.6b": QWEN3_06B, "32b": QWEN3_32B}
+
+
+def movudra_sizes(width=2048, repeats=2, window=4096, vocab=32768):
+    """A Movudra configuration at sizes that resemble real layers: per repeat one gated delta layer (16 heads of
+    128 x 128) with a dense feed-forward of 4 x width, one latent attention layer (16 heads of 128 + 64, latent 512,
+    query latent 1,536) and one Mamba-2 layer (inner 2 x width in heads of 64, state 128, 8 groups), the last two with
+    64 routed experts of 1,408 of which a token uses 6."""
+    moe = {"kind": "moe", "expert": {"ff": 1408}, "router": {"experts": 64, "top": 6}}
+    delta = {"type": "channel_delta", "mixer": {"conv": 4, "dim": 128, "heads": width // 128, "kv_heads": width // 128, "vdim": 128},
+             "mlp": {"kind": "dense", "ff": 4 * width}}
+    latent = {"type": "latent_attention", "mlp": moe,
+              "mixer": {"dim": 128, "heads": width // 128, "kv_rank": 512, "q_rank": 1536, "rot_dim": 64, "vdim": 128,
+                        "scale": 192 ** -0.5, "mask": {"size": window},
+                        "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0, "fast": 32.0, "original": 4096, "slow": 1.0}}}}
+    mamba = {"type": "mamba2", "mlp": moe,
+             "mixer": {"conv": 4, "groups": 8, "heads": 2 * width // 64, "norm_groups": 8, "state": 128, "vdim": 64}}
+    return {"architecture": "Movudra", "layers": [delta, latent, mamba] * repeats, "norm": {"eps": 1e-5},
+            "vocab": vocab, "width": width}
+
+
+def qwen3_beside(width=2048, layers=6, vocab=32768):
+    """The closest model the library had, at the same width, depth and vocabulary: Qwen3 layers with 16 heads of 128
+    (8 key/value heads) and a gated feed-forward of 3 x width."""
+    return dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=width // 128,
+                num_key_value_heads=width // 256, intermediate_size=3 * width, vocab_size=vocab)
 N_CTX = 4096
 PROMPT_LEN = 1024
 PREFILL_TOKENS = 2048
@@ -287,6 +312,107 @@ def large_model_workload(torch, np, peaks) -> dict:
     return out
 
 
+def _tensor_bytes(obj, seen) -> int:
+    import torch
+    total = 0
+    for v in vars(obj).values():
+        if isinstance(v, torch.Tensor) and v.dim() >= 2 and v.data_ptr() not in seen:
+            seen.add(v.data_ptr())
+            total += v.numel() * v.element_size()
+    return total
+
+
+def step_weight_bytes(engine, batch: int) -> int:
+    """Bytes of the matrices that one decode step of ``batch`` tokens reads at most once each: every bound matrix of the
+    mixers and feed-forwards and the head; of routed experts only as many as the batch can choose."""
+    seen, total = set(), 0
+    for block in engine.model.blocks:
+        total += _tensor_bytes(block.mixer, seen)
+        ffn = getattr(block, "ffn", None)
+        if ffn is None:
+            continue
+        if hasattr(ffn, "experts"):
+            per_expert = (ffn.w_gate_up[0].numel() + ffn.w_down[0].numel()) * ffn.w_down.element_size()
+            total += min(ffn.experts, batch * ffn.top) * per_expert + ffn.w_router.numel() * ffn.w_router.element_size()
+        else:
+            total += _tensor_bytes(ffn, seen)
+    return total + engine.model.head.weight.numel() * engine.model.head.weight.element_size()
+
+
+def time_parts(engine, torch, rng, n_tokens: int, batch: int, prompt: int = 0, reps: int = 5) -> dict:
+    """Median microseconds of every layer's mixer and feed-forward alone, in a step of ``batch`` sequences that bring
+    ``n_tokens`` tokens each after ``prompt`` cached ones: the parts' own forward calls on the step's context."""
+    from questwend_b200.engine.engine import StepEntry
+    slots = engine.open_sequences(batch)
+    V = engine.vocab_size
+    if prompt:
+        engine.step([StepEntry(s, rng.integers(0, V, prompt).tolist(), []) for s in slots])
+    ctx, _ = engine.build_context([StepEntry(s, rng.integers(0, V, n_tokens).tolist(), []) for s in slots])
+    T = ctx.n_tokens
+    x = torch.randn(T, engine.plan.hidden_size, device=engine.device).to(engine.dtype)
+    for position in engine.model._positions.values():
+        position.prepare(ctx)
+    out = {}
+
+    def timed(fn):
+        times = []
+        for _ in range(reps + 1):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3)
+        return round(statistics.median(times[1:]), 1)
+
+    seen = set()
+    for i, run in enumerate(engine.model.schedule):
+        block = engine.model.blocks[run.layer]
+        unit = engine.unit_caches[i]
+        name = type(block.mixer).__name__
+        if name not in seen:
+            seen.add(name)
+            if getattr(block.mixer, "adds_to_residual", False):
+                out[name + "_us"] = timed(lambda: block.mixer.forward(x, ctx, unit, residual=None))
+            else:
+                out[name + "_us"] = timed(lambda: block.mixer.forward(x, ctx, unit))
+        ffn = getattr(block, "ffn", None)
+        if ffn is not None and type(ffn).__name__ not in seen:
+            seen.add(type(ffn).__name__)
+            out[type(ffn).__name__ + "_us"] = timed(lambda: ffn.forward(x, ctx))
+    engine.close_sequences(slots)
+    return out
+
+
+def movudra_workload(torch, np, peaks, steps: int, warmup: int) -> dict:
+    """Prefill and decode of the Movudra design at real layer sizes (``movudra_sizes``), and of Qwen3 layers of the same
+    width, depth and vocabulary (``qwen3_beside``): tokens a second for a 2,048-token prompt and for graph-replayed
+    decode steps at batch 1 and 8 after 1,024-token prompts, the decode steps against the HBM roofline of the matrices
+    they must read, and the time of every kind of mixer and feed-forward alone in both kinds of step."""
+    from questwend_b200.config.registry import config_from_dict
+    from questwend_b200.engine.engine import Engine
+    out = {}
+    for name, cfgd in (("movudra", movudra_sizes()), ("qwen3_same_size", qwen3_beside())):
+        engine = Engine.from_config(config_from_dict(cfgd), seed=0, dtype="bfloat16", max_tokens=8 * (PROMPT_LEN + 512) + 4096,
+                                    max_seq_len=N_CTX, max_batch=9)
+        rng = np.random.default_rng(1)
+        point = {"parameters": engine.describe()["parameters"], "layers": len(engine.model.blocks)}
+        ms = time_prefill(engine, torch, rng, PREFILL_TOKENS)
+        point["prefill_2048"] = {"ms": round(ms, 3), "tok_s": round(PREFILL_TOKENS / (ms / 1e3), 1)}
+        for batch in (1, 8):
+            r = decode_run(engine, torch, batch, warmup, steps, rng)
+            wbytes = step_weight_bytes(engine, batch)
+            point[f"decode_b{batch}"] = {"ms_per_step": round(r["ms_per_step"], 4), "tok_s": round(r["tok_s"], 1),
+                                         "launches_per_step": r["launches_per_step"], "weight_bytes": wbytes,
+                                         "hbm_roofline_frac": round(wbytes / (r["ms_per_step"] / 1e3) / (peaks["hbm_gbs"] * 1e9), 3)}
+        point["parts_prefill_2048"] = time_parts(engine, torch, rng, PREFILL_TOKENS, 1)
+        point["parts_decode_b8"] = time_parts(engine, torch, rng, 1, 8, prompt=PROMPT_LEN)
+        out[name] = point
+        release(engine, torch)
+    return out
+
+
 def reference_arm(args) -> int:
     """kishida/questwend itself, unmodified, through its own public classes (baseline/ref_bench.cpp), on the same sizes.
     Nothing of questwend_b200 is imported on this path."""
@@ -379,7 +505,9 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--model", default="8b", choices=sorted(MODELS))
+    ap.add_argument("--model", default="8b", choices=sorted(MODELS) + ["movudra"],
+                    help="8b: the benchmark; 0.6b, 32b: its other workloads alone; movudra: the Movudra design at real layer "
+                         "sizes beside Qwen3 layers of the same width and depth")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64, the e2e run and the other models")
@@ -403,6 +531,11 @@ def main() -> int:
     import questwend_b200 as qw
 
     peaks, peak_source = load_peaks()
+    if args.model == "movudra":
+        print(json.dumps({"metric": "Movudra at real layer sizes beside Qwen3 layers of equal width and depth", "n_gpus": 1,
+                          "dtype": "bf16", "data": "synthetic: seeded random weights and uniform random token ids",
+                          "peaks": peak_source, "points": movudra_workload(torch, np, peaks, steps, warmup)}))
+        return 0
     if args.model != "8b":                      # one of the other workloads alone, as a line of its own
         points = small_model_workload(torch, np, peaks) if args.model == "0.6b" else large_model_workload(torch, np, peaks)
         print(json.dumps({"metric": f"Qwen3-{args.model.upper()} sizes workload", "n_gpus": 1, "dtype": "bf16",

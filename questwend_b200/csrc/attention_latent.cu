@@ -90,7 +90,8 @@ template <typename T, int NC>       // NC * 32 >= L
 __global__ void latent_attn_kernel(const float* __restrict__ q_abs, const float* __restrict__ q_rot, const T* __restrict__ pool,
                                    const int* __restrict__ page_table, const int* __restrict__ cu_seqlens,
                                    const int* __restrict__ pos0, const float* __restrict__ sink, T* __restrict__ out, int n_tok,
-                                   int H, int L, int R, int page_size, int table_width, float scale, int window) {
+                                   int H, int L, int R, int page_size, int table_width, float scale, int window,
+                                   int run_keys, int max_runs, float* __restrict__ part_acc, float* __restrict__ part_ml) {
     pdl_wait();
     pdl_launch_dependents();
     constexpr int ROWS = 16, BK = 32, RPW = 4;
@@ -99,8 +100,10 @@ __global__ void latent_attn_kernel(const float* __restrict__ q_abs, const float*
     float* Qs = smem;                       // [ROWS][dk], scaled
     float* Ks = Qs + ROWS * dk;             // [BK][dk + 1]
 
-    const int HB = min(H, ROWS), TQ = ROWS / HB;
-    const int b = blockIdx.z, h0 = blockIdx.y * HB, q0 = blockIdx.x * TQ;
+    // run_keys > 0: a step of one token per sequence, the keys cut into runs of run_keys; blockIdx.x is the run, and the
+    // block leaves its running maximum, sum and unnormalised accumulator for latent_combine_kernel
+    const int HB = min(H, ROWS), TQ = run_keys > 0 ? 1 : ROWS / HB;
+    const int b = blockIdx.z, h0 = blockIdx.y * HB, q0 = run_keys > 0 ? 0 : blockIdx.x * TQ;
     const int t0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - t0;
     if (q0 >= n_new) return;
     const int nq = min(TQ, n_new - q0), nh = min(HB, H - h0);
@@ -125,8 +128,13 @@ __global__ void latent_attn_kernel(const float* __restrict__ q_abs, const float*
 #pragma unroll
         for (int c = 0; c < NC; ++c) acc[i][c] = 0.f;
     }
-    const int k_last = p0 + q0 + nq - 1;
-    const int k_first = window > 0 ? max(0, p0 + q0 - window + 1) : 0;
+    int k_last = p0 + q0 + nq - 1;
+    int k_first = window > 0 ? max(0, p0 + q0 - window + 1) : 0;
+    if (run_keys > 0) {
+        k_first = max(k_first, (int)blockIdx.x * run_keys);
+        k_last = min(k_last, ((int)blockIdx.x + 1) * run_keys - 1);
+        if (k_first > k_last || (int)blockIdx.x >= max_runs) return;         // no visible key in this run (whole block)
+    }
     const int* pages = page_table + (size_t)b * table_width;
 
     for (int kt = (k_first / BK) * BK; kt <= k_last; kt += BK) {
@@ -187,6 +195,16 @@ __global__ void latent_attn_kernel(const float* __restrict__ q_abs, const float*
         const int qi = r / HB, hi = r - qi * HB;
         if (qi >= nq || hi >= nh) continue;
         const int h = h0 + hi;
+        if (run_keys > 0) {
+            const size_t at = ((size_t)b * H + h) * max_runs + blockIdx.x;
+            if (lane == 0) { part_ml[2 * at] = m[i]; part_ml[2 * at + 1] = l[i]; }
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                const int d = lane + 32 * c;
+                if (d < L) part_acc[at * L + d] = acc[i][c];
+            }
+            continue;
+        }
         float mi = m[i], li = l[i], rescale = 1.f;
         if (sink) {                                             // one more term in the denominator, with no value
             const float sk = sink[h];
@@ -204,15 +222,43 @@ __global__ void latent_attn_kernel(const float* __restrict__ q_abs, const float*
     }
 }
 
+// The runs of one (sequence, head) merged: out = sum_r acc_r e^(m_r - M) / (sum_r l_r e^(m_r - M) + e^(sink - M)),
+// M = max(m_r, sink), over the runs that hold a visible key, in their order.  grid (H, B).
+template <typename T>
+__global__ void latent_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                      const int* __restrict__ pos0, const float* __restrict__ sink, T* __restrict__ out,
+                                      int n_tok, int H, int L, int window, int run_keys, int max_runs) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int len = pos0[b] + 1;
+    const int k_lo = window > 0 ? max(0, len - window) : 0;
+    const int r0 = k_lo / run_keys, r1 = min((len - 1) / run_keys, max_runs - 1);
+    const size_t base = ((size_t)b * H + h) * max_runs;
+    float M = sink ? sink[h] : -INFINITY;
+    for (int r = r0; r <= r1; ++r) M = fmaxf(M, part_ml[2 * (base + r)]);
+    float denom = sink ? expf(sink[h] - M) : 0.f;
+    for (int r = r0; r <= r1; ++r) denom += part_ml[2 * (base + r) + 1] * expf(part_ml[2 * (base + r)] - M);
+    const float inv = 1.f / denom;
+    for (int d = threadIdx.x; d < L; d += blockDim.x) {
+        float v = 0.f;
+        for (int r = r0; r <= r1; ++r) v += part_acc[(base + r) * L + d] * expf(part_ml[2 * (base + r)] - M);
+        out[((size_t)h * n_tok + b) * L + d] = from_f32<T>(v * inv);
+    }
+}
+
+#define QWB_LATENT_RUN_KEYS 64
+
 template <typename T>
 static int launch_latent_attn(const float* q_abs, const float* q_rot, const void* pool, const int* page_table,
                               const int* cu_seqlens, const int* pos0, const float* sink, void* out, int B, int n_tok,
                               int max_new, int H, int L, int R, int page_size, int table_width, float scale, int window,
-                              cudaStream_t stream) {
+                              int max_runs, float* part_acc, float* part_ml, cudaStream_t stream) {
     const int dk = L + R;
     const size_t smem = ((size_t)16 * dk + 32 * (dk + 1)) * sizeof(float);
     const int HB = H < 16 ? H : 16, TQ = 16 / HB;
-    dim3 grid((max_new + TQ - 1) / TQ, (H + HB - 1) / HB, B);
+    const int run_keys = max_runs > 0 ? QWB_LATENT_RUN_KEYS : 0;
+    dim3 grid(max_runs > 0 ? max_runs : (max_new + TQ - 1) / TQ, (H + HB - 1) / HB, B);
     const int nc = (L + 31) / 32;
 #define QWB_LAUNCH_LATENT(NC)                                                                                          \
     do {                                                                                                               \
@@ -221,33 +267,49 @@ static int launch_latent_attn(const float* q_abs, const float* q_rot, const void
             if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "latent_attn: %s", cudaGetErrorString(e));             \
         }                                                                                                              \
         qwb_launch(latent_attn_kernel<T, NC>, grid, 128, smem, stream, q_abs, q_rot, (const T*)pool, page_table,       \
-                   cu_seqlens, pos0, sink, (T*)out, n_tok, H, L, R, page_size, table_width, scale, window);            \
+                   cu_seqlens, pos0, sink, (T*)out, n_tok, H, L, R, page_size, table_width, scale, window, run_keys,   \
+                   max_runs, part_acc, part_ml);                                                                      \
     } while (0)
     if (nc <= 2) QWB_LAUNCH_LATENT(2);
     else if (nc <= 4) QWB_LAUNCH_LATENT(4);
     else if (nc <= 8) QWB_LAUNCH_LATENT(8);
     else QWB_LAUNCH_LATENT(16);
 #undef QWB_LAUNCH_LATENT
-    return qwb_check_launch("latent_attn");
+    if (int rc = qwb_check_launch("latent_attn")) return rc;
+    if (max_runs > 0) {
+        qwb_launch(latent_combine_kernel<T>, dim3(H, B), 128, 0, stream, (const float*)part_acc, (const float*)part_ml, pos0, sink,
+                   (T*)out, n_tok, H, L, window, run_keys, max_runs);
+        return qwb_check_launch("latent_combine");
+    }
+    return 0;
 }
 
 #define QWB_LATENT_MAX_L 512
 #define QWB_LATENT_MAX_ROW 1024
 
+// max_runs > 0: every sequence brings one token (n_tok = B) and no sequence holds more than max_runs * 64 keys after the
+// step; the keys are cut into runs of 64 (by the key's index, whatever else is in the batch), a block a run, and merged.
+// scratch: max_runs * B * H * (L + 2) floats.
+extern "C" int qwb_latent_run_keys() { return QWB_LATENT_RUN_KEYS; }
+
 extern "C" int qwb_latent_attn(const float* q_abs, const float* q_rot, const void* pool, const int* page_table,
                                const int* cu_seqlens, const int* pos0, const float* sink, void* out, int dtype, int B,
                                int n_tok, int max_new, int H, int L, int R, int page_size, int table_width, float scale,
-                               int window, cudaStream_t stream) {
+                               int window, int max_runs, float* scratch, cudaStream_t stream) {
     if (B <= 0 || n_tok <= 0 || max_new <= 0) return 0;
     if (H <= 0 || L <= 0 || R < 0 || L > QWB_LATENT_MAX_L || L + R > QWB_LATENT_MAX_ROW)
         return qwb_fail(QWB_ERR_ARG, "latent_attn: %d heads, latent %d (up to %d) + rotated %d (row up to %d)", H, L, QWB_LATENT_MAX_L, R, QWB_LATENT_MAX_ROW);
     if (page_size <= 0 || table_width <= 0) return qwb_fail(QWB_ERR_ARG, "latent_attn: bad page size %d or table width %d", page_size, table_width);
-    if (B > 65535 || H > 65535 * 16) return qwb_fail(QWB_ERR_ARG, "latent_attn: batch %d or heads %d are too many", B, H);
+    if (B > 65535 || H > 65535) return qwb_fail(QWB_ERR_ARG, "latent_attn: batch %d or heads %d are too many", B, H);
+    if (max_runs > 0 && (max_new != 1 || n_tok != B || !scratch))
+        return qwb_fail(QWB_ERR_ARG, "latent_attn: runs of keys are for steps of one token per sequence, with scratch memory");
+    float* part_acc = scratch;
+    float* part_ml = max_runs > 0 ? scratch + (size_t)max_runs * B * H * L : nullptr;
     if (dtype == QWB_DT_F32)
         return launch_latent_attn<float>(q_abs, q_rot, pool, page_table, cu_seqlens, pos0, sink, out, B, n_tok, max_new, H, L, R,
-                                         page_size, table_width, scale, window, stream);
+                                         page_size, table_width, scale, window, max_runs, part_acc, part_ml, stream);
     if (dtype == QWB_DT_BF16)
         return launch_latent_attn<bf16>(q_abs, q_rot, pool, page_table, cu_seqlens, pos0, sink, out, B, n_tok, max_new, H, L, R,
-                                        page_size, table_width, scale, window, stream);
+                                        page_size, table_width, scale, window, max_runs, part_acc, part_ml, stream);
     return qwb_fail(QWB_ERR_ARG, "latent_attn: unknown dtype %d", dtype);
 }

@@ -7,7 +7,8 @@
 //
 // The products read each chosen expert's rows straight from the stacked weights (Wgu [E, 2F, D]: gate rows, then up
 // rows; Wd [E, D, F]): a warp per output feature, 32-bit sums.  This is the form for a step of few tokens, where every
-// token's experts are streamed once; prompts use it too (the experts of a long prompt come from L2).
+// token's experts are streamed once, and for the 32-bit engine.  Many bfloat16 tokens are sorted by expert instead
+// and go through a library grouped product; moe_gated_act and moe_combine are the kernels around it.
 #include "common.cuh"
 
 #define QWB_MOE_MAX_TOP 16
@@ -130,4 +131,48 @@ extern "C" int qwb_moe_experts(const void* x, const void* wgu, const void* wd, c
         return qwb_fail(QWB_ERR_ARG, "moe_experts: unknown dtype %d", dtype);
     }
     return qwb_check_launch("moe_experts");
+}
+
+// ---------------------------------------------------------------------------------
+// Around a grouped product over token copies sorted by expert (bfloat16):
+//   moe_gated_act  act[s, f] = silu(gu[s, f]) * gu[s, F + f]           gu [S, 2F] -> act [S, F]
+//   moe_combine    out[t, :] = sum_k weight[t, k] * y[place[t, k], :]   y [S, D] -> out float [T, D]
+// place[t, k] is the row of token t's k-th copy in the sorted order.
+// ---------------------------------------------------------------------------------
+__global__ void moe_gated_act_kernel(const bf16* __restrict__ gu, bf16* __restrict__ act, size_t n, int F) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / F, f = i - r * F;
+        const float g = to_f32(gu[r * 2 * F + f]), u = to_f32(gu[r * 2 * F + F + f]);
+        act[i] = from_f32<bf16>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+extern "C" int qwb_moe_gated_act(const void* gu, void* act, int S, int F, cudaStream_t stream) {
+    if (S <= 0 || F <= 0) return 0;
+    const size_t n = (size_t)S * F;
+    const int block = 256, grid = (int)((n + block - 1) / block < 148 * 16 ? (n + block - 1) / block : 148 * 16);
+    qwb_launch(moe_gated_act_kernel, grid, block, 0, stream, (const bf16*)gu, (bf16*)act, n, F);
+    return qwb_check_launch("moe_gated_act");
+}
+
+__global__ void moe_combine_kernel(const bf16* __restrict__ y, const long long* __restrict__ place, const float* __restrict__ weight,
+                                   float* __restrict__ out, int D, int top) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float total = 0.f;
+        for (int k = 0; k < top; ++k)
+            total += weight[(size_t)t * top + k] * to_f32(y[(size_t)place[(size_t)t * top + k] * D + d]);
+        out[(size_t)t * D + d] = total;
+    }
+}
+
+extern "C" int qwb_moe_combine(const void* y, const long long* place, const float* weight, float* out, int T, int D, int top,
+                               cudaStream_t stream) {
+    if (T <= 0 || D <= 0) return 0;
+    qwb_launch(moe_combine_kernel, T, D >= 1024 ? 256 : 128, 0, stream, (const bf16*)y, place, weight, out, D, top);
+    return qwb_check_launch("moe_combine");
 }

@@ -72,85 +72,116 @@ extern "C" int qwb_short_conv(const float* x, int ld, const float* w, const floa
 }
 
 // ---------------------------------------------------------------------------------
-// Mamba-2 recurrence.  Per head h (group g = h / (H / G)), per token:
-//     dt = softplus(dt_raw + dt_bias[h]);  S = exp(-exp(A_log[h]) dt) S + dt B x^T;  y = S^T C + D[h] x
-// S is N x P (state x value size).  One block per (head, sequence); thread (part, p) keeps PER rows of column p
-// of S in registers: rows part * PER .. part * PER + PER - 1.  The parts' sums meet in shared memory.
-//   xbc [T, ldx] float: x [H * P] | B [G * N] | C [G * N] (after convolution and SiLU)
-//   dt_raw: column h of a [T, ld_dt] matrix;  state [slots, H, N, P];  y [T, H * P]
+// The recurrences keep, per head, a state matrix S of rows x P (state or key size x value size) whose columns never
+// meet: column p is read and written with the token's value p only.  So one WARP owns one column: lane l keeps rows
+// l * PER .. l * PER + PER - 1 in registers, a sum over the rows is a shuffle reduction, and there is no shared
+// memory and no barrier; a block is four columns of one head, the grid (columns / 4, heads, sequences).  The state
+// is stored column by column, [slots, H, P, rows], so that a warp's piece is one contiguous run.  A token's vectors
+// are asked for one token ahead.
 // ---------------------------------------------------------------------------------
-template <int PER>
-__global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const float* __restrict__ dt_raw, int ld_dt,
-                                const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dskip,
-                                float* state, const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
-                                float* __restrict__ y, int H, int P, int N, int G, int write_state) {
+#define QWB_SCAN_WARPS 4
+#define QWB_SCAN_MAX_PER 16
+
+// PER consecutive floats from base[n0 ..], zeros from `limit` on; VEC: n0, limit and base allow 16-byte loads.
+template <int PER, bool VEC>
+__device__ __forceinline__ void load_rows(const float* __restrict__ base, int n0, int limit, float* out) {
+    if (VEC) {
+#pragma unroll
+        for (int k = 0; k < PER; k += 4) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (n0 + k < limit) v = *reinterpret_cast<const float4*>(base + n0 + k);
+            out[k] = v.x; out[k + 1] = v.y; out[k + 2] = v.z; out[k + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < PER; ++k) out[k] = n0 + k < limit ? base[n0 + k] : 0.f;
+    }
+}
+
+// Mamba-2.  Per head h (group g = h / (H / G)), per token:
+//     dt = softplus(dt_raw + dt_bias[h]);  S = exp(-exp(A_log[h]) dt) S + dt B x^T;  y = S^T C + D[h] x
+//   xbc [T, ldx] float: x [H * P] | B [G * N] | C [G * N] (after convolution and SiLU)
+//   dt_raw: column h of a [T, ld_dt] matrix;  state [slots, H, P, N];  y [T, H * P]
+template <int PER, bool VEC>
+__global__ void __launch_bounds__(32 * QWB_SCAN_WARPS)
+ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const float* __restrict__ dt_raw, int ld_dt,
+                const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dskip,
+                float* __restrict__ state, const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                float* __restrict__ y, int H, int P, int N, int G, int write_state) {
     pdl_wait();
     pdl_launch_dependents();
-    extern __shared__ float red[];                      // [2][parts][P]
-    const int h = blockIdx.x, b = blockIdx.y;
-    const int parts = (N + PER - 1) / PER;
-    const int p = threadIdx.x % P, part = threadIdx.x / P;
+    const int lane = threadIdx.x & 31;
+    const int p = blockIdx.x * QWB_SCAN_WARPS + (threadIdx.x >> 5), h = blockIdx.y, b = blockIdx.z;
+    if (p >= P) return;
     const int g = h / (H / G);
     const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
-    const int n0 = part * PER;
-    float* S = state + (((size_t)slots[b] * H + h) * N) * P;
+    const int n0 = lane * PER;
+    float* S = state + (((size_t)slots[b] * H + h) * P + p) * N;
     float s[PER];
-#pragma unroll
-    for (int k = 0; k < PER; ++k) s[k] = n0 + k < N ? S[(size_t)(n0 + k) * P + p] : 0.f;
+    load_rows<PER, VEC>(S, n0, N, s);
     const float a = -expf(A_log[h]), dskip = Dskip[h], bias = dt_bias[h];
     const int inner = H * P;
-    int buf = 0;
+    float Bn[PER], Cn[PER], dt_n = 0.f, x_n = 0.f;
+    if (t0 < t1) {
+        const float* row = xbc + (size_t)t0 * ldx;
+        load_rows<PER, VEC>(row + inner + g * N, n0, N, Bn);
+        load_rows<PER, VEC>(row + inner + (G + g) * N, n0, N, Cn);
+        dt_n = dt_raw[(size_t)t0 * ld_dt + h];
+        x_n = row[h * P + p];
+    }
     for (int t = t0; t < t1; ++t) {
-        const float* row = xbc + (size_t)t * ldx;
-        const float dt = softplus_f(dt_raw[(size_t)t * ld_dt + h] + bias);
+        float Bt[PER], Ct[PER];
+#pragma unroll
+        for (int k = 0; k < PER; ++k) { Bt[k] = Bn[k]; Ct[k] = Cn[k]; }
+        const float dt_in = dt_n, xv = x_n;
+        if (t + 1 < t1) {
+            const float* row = xbc + (size_t)(t + 1) * ldx;
+            load_rows<PER, VEC>(row + inner + g * N, n0, N, Bn);
+            load_rows<PER, VEC>(row + inner + (G + g) * N, n0, N, Cn);
+            dt_n = dt_raw[(size_t)(t + 1) * ld_dt + h];
+            x_n = row[h * P + p];
+        }
+        const float dt = softplus_f(dt_in + bias);
         const float decay = expf(a * dt);
-        const float xv = row[h * P + p];
         const float dtx = dt * xv;
-        const float* Bt = row + inner + g * N + n0;
-        const float* Ct = Bt + G * N;
         float acc = 0.f;
 #pragma unroll
         for (int k = 0; k < PER; ++k) {
-            if (n0 + k < N) {
-                s[k] = decay * s[k] + dtx * Bt[k];
-                acc += s[k] * Ct[k];
-            }
+            s[k] = decay * s[k] + dtx * Bt[k];
+            acc += s[k] * Ct[k];
         }
-        red[(buf * parts + part) * P + p] = acc;
-        __syncthreads();
-        if (part == 0) {
-            float total = 0.f;
-            for (int q = 0; q < parts; ++q) total += red[(buf * parts + q) * P + p];
-            y[(size_t)t * inner + h * P + p] = total + dskip * xv;
-        }
-        buf ^= 1;
+        acc = warp_sum(acc);
+        if (lane == 0) y[(size_t)t * inner + h * P + p] = acc + dskip * xv;
     }
     if (write_state) {
 #pragma unroll
         for (int k = 0; k < PER; ++k)
-            if (n0 + k < N) S[(size_t)(n0 + k) * P + p] = s[k];
+            if (n0 + k < N) S[n0 + k] = s[k];
     }
 }
 
-static int scan_rows_per_thread(int rows, int cols) {      // 16, 32 or 64 rows of the state per thread; 0: too large
-    for (int per = 16; per <= 64; per *= 2)
-        if ((size_t)cols * ((rows + per - 1) / per) <= 1024) return per;
+static int scan_rows_per_lane(int rows) {      // 1, 2, 4, 8 or 16 rows of a column per lane; 0: too many rows
+    for (int per = 1; per <= QWB_SCAN_MAX_PER; per *= 2)
+        if (32 * per >= rows) return per;
     return 0;
 }
+static bool aligned16(const void* p) { return (uintptr_t)p % 16 == 0; }
 
 extern "C" int qwb_ssm_scan(const float* xbc, int ldx, const float* dt_raw, int ld_dt, const float* dt_bias, const float* A_log,
                             const float* Dskip, float* state, const int* cu_seqlens, const int* slots, float* y, int B,
                             int H, int P, int N, int G, int write_state, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (H <= 0 || P <= 0 || N <= 0 || G <= 0 || H % G) return qwb_fail(QWB_ERR_ARG, "ssm_scan: %d heads, %d groups, state %d x %d", H, G, N, P);
-    const int per = scan_rows_per_thread(N, P);
-    if (!per) return qwb_fail(QWB_ERR_ARG, "ssm_scan: a state of %d x %d per head is too large (value size x ceil(state / 64) <= 1024)", N, P);
-    if (B > 65535) return qwb_fail(QWB_ERR_ARG, "ssm_scan: %d sequences are too many", B);
-    const int parts = (N + per - 1) / per;
-    const size_t smem = (size_t)2 * parts * P * sizeof(float);
-    const dim3 grid(H, B);
-#define QWB_SSM(PER) qwb_launch(ssm_scan_kernel<PER>, grid, P * parts, smem, stream, xbc, ldx, dt_raw, ld_dt, dt_bias, A_log, Dskip, state, cu_seqlens, slots, y, H, P, N, G, write_state)
-    if (per == 16) QWB_SSM(16); else if (per == 32) QWB_SSM(32); else QWB_SSM(64);
+    const int per = scan_rows_per_lane(N);
+    if (!per) return qwb_fail(QWB_ERR_ARG, "ssm_scan: a state of %d rows per head is too large (up to %d)", N, 32 * QWB_SCAN_MAX_PER);
+    if (B > 65535 || H > 65535) return qwb_fail(QWB_ERR_ARG, "ssm_scan: %d sequences or %d heads are too many", B, H);
+    const dim3 grid((P + QWB_SCAN_WARPS - 1) / QWB_SCAN_WARPS, H, B);
+    const bool vec = per >= 4 && N % 4 == 0 && ldx % 4 == 0 && (H * P) % 4 == 0 && aligned16(xbc) && aligned16(state);
+#define QWB_SSM(PER, VEC) qwb_launch(ssm_scan_kernel<PER, VEC>, grid, 32 * QWB_SCAN_WARPS, 0, stream, xbc, ldx, dt_raw, ld_dt, dt_bias, A_log, Dskip, state, cu_seqlens, slots, y, H, P, N, G, write_state)
+    if (per == 1) QWB_SSM(1, false); else if (per == 2) QWB_SSM(2, false);
+    else if (per == 4) { if (vec) QWB_SSM(4, true); else QWB_SSM(4, false); }
+    else if (per == 8) { if (vec) QWB_SSM(8, true); else QWB_SSM(8, false); }
+    else { if (vec) QWB_SSM(16, true); else QWB_SSM(16, false); }
 #undef QWB_SSM
     return qwb_check_launch("ssm_scan");
 }
@@ -202,64 +233,63 @@ extern "C" int qwb_delta_prep(float* qkv, int ld, float* kq, const float* b_raw,
 
 // The recurrence, per head h (key head kh = h / (H / Hk)), per token, S is K x P:
 //     S = decay[:, None] * S;  u = beta (v - S^T k);  S = S + k u^T;  o = S^T q
-// o is formed as (decayed S)^T q + u (k . q), so that one meeting of the parts' sums per token is enough.
-// Threads as in ssm_scan_kernel: (part, p) keeps PER rows of column p.
-template <int PER>
-__global__ void delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ kq, const float* __restrict__ beta,
-                                  const float* __restrict__ decay, float* state, const int* __restrict__ cu_seqlens,
-                                  const int* __restrict__ slots, float* __restrict__ o, int H, int Hk, int K, int P, int write_state) {
+// o is formed as (decayed S)^T q + u (k . q), so that both sums over the rows are taken in one pass.  A warp per
+// column, as above; state [slots, H, P, K].
+template <int PER, bool VEC>
+__global__ void __launch_bounds__(32 * QWB_SCAN_WARPS)
+delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ kq, const float* __restrict__ beta,
+                  const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ cu_seqlens,
+                  const int* __restrict__ slots, float* __restrict__ o, int H, int Hk, int K, int P, int write_state) {
     pdl_wait();
     pdl_launch_dependents();
-    extern __shared__ float red[];                      // [2][2][parts][P]
-    const int h = blockIdx.x, b = blockIdx.y;
-    const int parts = (K + PER - 1) / PER;
-    const int p = threadIdx.x % P, part = threadIdx.x / P;
+    const int lane = threadIdx.x & 31;
+    const int p = blockIdx.x * QWB_SCAN_WARPS + (threadIdx.x >> 5), h = blockIdx.y, b = blockIdx.z;
+    if (p >= P) return;
     const int kh = h / (H / Hk);
     const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
-    const int n0 = part * PER;
-    float* S = state + (((size_t)slots[b] * H + h) * K) * P;
+    const int n0 = lane * PER;
+    float* S = state + (((size_t)slots[b] * H + h) * P + p) * K;
     float s[PER];
-#pragma unroll
-    for (int k = 0; k < PER; ++k) s[k] = n0 + k < K ? S[(size_t)(n0 + k) * P + p] : 0.f;
-    int buf = 0;
+    load_rows<PER, VEC>(S, n0, K, s);
+    const int v_at = 2 * Hk * K + h * P + p;
+    float kn[PER], qn[PER], gn[PER], v_n = 0.f, beta_n = 0.f, kq_n = 0.f;
+    if (t0 < t1) {
+        const float* row = qkv + (size_t)t0 * ld;
+        load_rows<PER, VEC>(row + kh * K, n0, K, qn);
+        load_rows<PER, VEC>(row + (Hk + kh) * K, n0, K, kn);
+        load_rows<PER, VEC>(decay + ((size_t)t0 * H + h) * K, n0, K, gn);
+        v_n = row[v_at]; beta_n = beta[(size_t)t0 * H + h]; kq_n = kq[(size_t)t0 * Hk + kh];
+    }
     for (int t = t0; t < t1; ++t) {
-        const float* row = qkv + (size_t)t * ld;
-        const float* qt = row + kh * K + n0;
-        const float* kt = row + (Hk + kh) * K + n0;
-        const float* gt = decay + ((size_t)t * H + h) * K + n0;
-        const float v = row[2 * Hk * K + h * P + p];
-        float kk[PER];
+        float kk[PER], qq[PER], gg[PER];
+#pragma unroll
+        for (int k = 0; k < PER; ++k) { kk[k] = kn[k]; qq[k] = qn[k]; gg[k] = gn[k]; }
+        const float v = v_n, bt = beta_n, kqv = kq_n;
+        if (t + 1 < t1) {
+            const float* row = qkv + (size_t)(t + 1) * ld;
+            load_rows<PER, VEC>(row + kh * K, n0, K, qn);
+            load_rows<PER, VEC>(row + (Hk + kh) * K, n0, K, kn);
+            load_rows<PER, VEC>(decay + ((size_t)(t + 1) * H + h) * K, n0, K, gn);
+            v_n = row[v_at]; beta_n = beta[(size_t)(t + 1) * H + h]; kq_n = kq[(size_t)(t + 1) * Hk + kh];
+        }
         float sk = 0.f, sq = 0.f;
 #pragma unroll
         for (int k = 0; k < PER; ++k) {
-            if (n0 + k < K) {
-                kk[k] = kt[k];
-                s[k] *= gt[k];
-                sk += s[k] * kk[k];
-                sq += s[k] * qt[k];
-            }
+            s[k] *= gg[k];
+            sk += s[k] * kk[k];
+            sq += s[k] * qq[k];
         }
-        float* r = red + (size_t)buf * 2 * parts * P;
-        r[part * P + p] = sk;
-        r[(parts + part) * P + p] = sq;
-        __syncthreads();
-        float tk = 0.f;
-        for (int q = 0; q < parts; ++q) tk += r[q * P + p];
-        const float u = beta[(size_t)t * H + h] * (v - tk);
+        sk = warp_sum(sk);
+        sq = warp_sum(sq);
+        const float u = bt * (v - sk);
 #pragma unroll
-        for (int k = 0; k < PER; ++k)
-            if (n0 + k < K) s[k] += kk[k] * u;
-        if (part == 0) {
-            float tq = 0.f;
-            for (int q = 0; q < parts; ++q) tq += r[(parts + q) * P + p];
-            o[((size_t)t * H + h) * P + p] = tq + u * kq[(size_t)t * Hk + kh];
-        }
-        buf ^= 1;
+        for (int k = 0; k < PER; ++k) s[k] += kk[k] * u;
+        if (lane == 0) o[((size_t)t * H + h) * P + p] = sq + u * kqv;
     }
     if (write_state) {
 #pragma unroll
         for (int k = 0; k < PER; ++k)
-            if (n0 + k < K) S[(size_t)(n0 + k) * P + p] = s[k];
+            if (n0 + k < K) S[n0 + k] = s[k];
     }
 }
 
@@ -268,14 +298,16 @@ extern "C" int qwb_delta_scan(const float* qkv, int ld, const float* kq, const f
                               int write_state, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (H <= 0 || Hk <= 0 || K <= 0 || P <= 0 || H % Hk) return qwb_fail(QWB_ERR_ARG, "delta_scan: %d heads, %d key heads, state %d x %d", H, Hk, K, P);
-    const int per = scan_rows_per_thread(K, P);
-    if (!per) return qwb_fail(QWB_ERR_ARG, "delta_scan: a state of %d x %d per head is too large (value size x ceil(key size / 64) <= 1024)", K, P);
-    if (B > 65535) return qwb_fail(QWB_ERR_ARG, "delta_scan: %d sequences are too many", B);
-    const int parts = (K + per - 1) / per;
-    const size_t smem = (size_t)4 * parts * P * sizeof(float);
-    const dim3 grid(H, B);
-#define QWB_DELTA(PER) qwb_launch(delta_scan_kernel<PER>, grid, P * parts, smem, stream, qkv, ld, kq, beta, decay, state, cu_seqlens, slots, o, H, Hk, K, P, write_state)
-    if (per == 16) QWB_DELTA(16); else if (per == 32) QWB_DELTA(32); else QWB_DELTA(64);
+    const int per = scan_rows_per_lane(K);
+    if (!per) return qwb_fail(QWB_ERR_ARG, "delta_scan: a state of %d rows per head is too large (up to %d)", K, 32 * QWB_SCAN_MAX_PER);
+    if (B > 65535 || H > 65535) return qwb_fail(QWB_ERR_ARG, "delta_scan: %d sequences or %d heads are too many", B, H);
+    const dim3 grid((P + QWB_SCAN_WARPS - 1) / QWB_SCAN_WARPS, H, B);
+    const bool vec = per >= 4 && K % 4 == 0 && ld % 4 == 0 && aligned16(qkv) && aligned16(decay) && aligned16(state);
+#define QWB_DELTA(PER, VEC) qwb_launch(delta_scan_kernel<PER, VEC>, grid, 32 * QWB_SCAN_WARPS, 0, stream, qkv, ld, kq, beta, decay, state, cu_seqlens, slots, o, H, Hk, K, P, write_state)
+    if (per == 1) QWB_DELTA(1, false); else if (per == 2) QWB_DELTA(2, false);
+    else if (per == 4) { if (vec) QWB_DELTA(4, true); else QWB_DELTA(4, false); }
+    else if (per == 8) { if (vec) QWB_DELTA(8, true); else QWB_DELTA(8, false); }
+    else { if (vec) QWB_DELTA(16, true); else QWB_DELTA(16, false); }
 #undef QWB_DELTA
     return qwb_check_launch("delta_scan");
 }

@@ -14,7 +14,7 @@ def head_dim_refusal(head_dim: int) -> str | None:
 
 
 CONV_MAX_TAPS = 8           # csrc/recurrent.cu: QWB_CONV_MAX_TAPS
-SCAN_MAX_THREADS = 1024     # a recurrent state's columns x ceil(rows / 64) threads of one block
+SCAN_MAX_ROWS = 512         # rows of a recurrent state's column that one warp keeps in registers (csrc/recurrent.cu)
 LATENT_MAX_RANK = 512       # csrc/attention_latent.cu: QWB_LATENT_MAX_L
 LATENT_MAX_ROW = 1024       # ... QWB_LATENT_MAX_ROW
 MOE_MAX_TOP = 16            # csrc/moe.cu: QWB_MOE_MAX_TOP
@@ -28,9 +28,9 @@ def conv_taps_refusal(taps: int) -> str | None:
 
 def state_matrix_refusal(rows: int, cols: int) -> str | None:
     """A recurrent state of rows x cols per head (state or key size x value size)."""
-    if rows <= 0 or cols <= 0 or cols * -(-rows // 64) > SCAN_MAX_THREADS:
-        return (f"the recurrence kernels keep a state of up to value size x ceil(key or state size / 64) <= "
-                f"{SCAN_MAX_THREADS} per head, not {rows} x {cols}")
+    if rows <= 0 or cols <= 0 or rows > SCAN_MAX_ROWS:
+        return (f"the recurrence kernels keep a state of up to {SCAN_MAX_ROWS} rows (key or state size) per head, "
+                f"not {rows} x {cols}")
     return None
 
 

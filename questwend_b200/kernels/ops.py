@@ -701,12 +701,12 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_col0: int, dt_bias, a_log, 
              heads: int, vdim: int, n_state: int, groups: int, write_state: bool = True) -> torch.Tensor:
     """The Mamba-2 recurrence over a step's tokens.  ``xbc`` float32 [T, heads * vdim + 2 * groups * n_state] (x | B | C,
     after convolution and SiLU); the raw step sizes are columns ``dt_col0 ..`` of float32 ``dt`` [T, ld]; ``state``
-    float32 [slots, heads, n_state, vdim] is read and written back.  Returns y float32 [T, heads * vdim]."""
+    float32 [slots, heads, vdim, n_state] (column by column) is read and written back.  Returns y float32 [T, heads * vdim]."""
     _need(xbc, "xbc", torch.float32, 2)
     _need(dt, "dt", torch.float32, 2)
     _need(state, "state", torch.float32, 4)
     T = xbc.shape[0]
-    if xbc.shape[1] != heads * vdim + 2 * groups * n_state or tuple(state.shape[1:]) != (heads, n_state, vdim):
+    if xbc.shape[1] != heads * vdim + 2 * groups * n_state or tuple(state.shape[1:]) != (heads, vdim, n_state):
         raise KernelError(f"ssm_scan: xbc {tuple(xbc.shape)}, state {tuple(state.shape)} do not fit {heads} heads of "
                           f"{vdim}, state {n_state}, {groups} groups")
     for name, t in (("dt_bias", dt_bias), ("A_log", a_log), ("D", d_skip)):
@@ -726,7 +726,7 @@ def delta_rule(qkv: torch.Tensor, b_raw: torch.Tensor, b_col0: int, a_raw: torch
     """The gated delta rule with a decay per head and key channel, over a step's tokens.  ``qkv`` float32
     [T, 2 * key_heads * key_dim + heads * vdim] (q | k | v after convolution and SiLU; q and k are made unit vectors
     in place, q times ``q_scale``); columns ``b_col0 .. b_col0 + heads`` of ``b_raw`` [T, ld] and ``a_raw``
-    [T, heads * key_dim] are the raw write strengths and decays; ``state`` float32 [slots, heads, key_dim, vdim].  Returns o float32 [T, heads * vdim]."""
+    [T, heads * key_dim] are the raw write strengths and decays; ``state`` float32 [slots, heads, vdim, key_dim] (column by column).  Returns o float32 [T, heads * vdim]."""
     _need(qkv, "qkv", torch.float32, 2)
     _need(b_raw, "b_raw", torch.float32, 2)
     _need(a_raw, "a_raw", torch.float32, 2)
@@ -735,7 +735,7 @@ def delta_rule(qkv: torch.Tensor, b_raw: torch.Tensor, b_col0: int, a_raw: torch
     _need(a_log, "A_log", torch.float32, 1)
     T = qkv.shape[0]
     if (qkv.shape[1] != 2 * key_heads * key_dim + heads * vdim or b_raw.shape[0] != T or b_col0 + heads > b_raw.shape[1]
-            or tuple(a_raw.shape) != (T, heads * key_dim) or tuple(state.shape[1:]) != (heads, key_dim, vdim)
+            or tuple(a_raw.shape) != (T, heads * key_dim) or tuple(state.shape[1:]) != (heads, vdim, key_dim)
             or dt_bias.numel() != heads * key_dim or a_log.numel() != heads):
         raise KernelError(f"delta_rule: qkv {tuple(qkv.shape)}, b {tuple(b_raw.shape)}, a {tuple(a_raw.shape)}, state "
                           f"{tuple(state.shape)} do not fit {heads} heads ({key_heads} key heads) of {key_dim} x {vdim}")
@@ -776,6 +776,7 @@ def gated_part_norm(y: torch.Tensor, gate: torch.Tensor, gate_col0: int, weight:
 # ----------------------------------------------------------------------------- latent attention
 LATENT_MAX_RANK = 512       # csrc/attention_latent.cu: QWB_LATENT_MAX_L
 LATENT_MAX_ROW = 1024       # ... QWB_LATENT_MAX_ROW: latent + rotated key part
+LATENT_RUN_KEYS = 64        # ... QWB_LATENT_RUN_KEYS: keys per block in a step of one token per sequence
 
 
 def latent_prep(q: torch.Tensor, dkv: torch.Tensor, c_weight: torch.Tensor, cos, sin, ctx, page_table, pool,
@@ -829,9 +830,16 @@ def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, pool: torch.Tenso
         if sink.numel() != H:
             raise KernelError(f"latent_attention: {sink.numel()} sinks for {H} heads")
     out = torch.empty((H, T, L), dtype=pool.dtype, device=q_abs.device)
+    max_runs, scratch = 0, None
+    if ctx.single_token and ctx.max_len > LATENT_RUN_KEYS:
+        # one token per sequence over more than one run of keys: a block a run (cut by the key's index, so a sequence's
+        # result does not depend on the batch), then a merge; ctx.max_len bounds every sequence's length
+        max_runs = -(-ctx.max_len // LATENT_RUN_KEYS)
+        scratch = torch.empty((max_runs * T * H * (L + 2),), dtype=torch.float32, device=q_abs.device)
     _call("attention_latent", "qwb_latent_attn", _ptr(q_abs), _ptr(q_rot), _ptr(pool), _ptr(page_table), _ptr(ctx.cu_seqlens),
           _ptr(ctx.pos0), _ptr(sink), _ptr(out), _i(_dt(pool.dtype)), _i(ctx.n_seqs), _i(T), _i(ctx.max_new), _i(H), _i(L),
-          _i(R), _i(pool.shape[2]), _i(page_table.shape[1]), _f(scale), _i(window), _stream())
+          _i(R), _i(pool.shape[2]), _i(page_table.shape[1]), _f(scale), _i(window), _i(max_runs), _ptr(scratch), _stream(),
+          kernels=2 if max_runs else 1)
     return out
 
 
@@ -875,6 +883,46 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
         _call("moe", "qwb_moe_experts", _ptr(x[t0:t0 + n]), _ptr(w_gate_up), _ptr(w_down), _ptr(chosen[t0:t0 + n]),
               _ptr(weight[t0:t0 + n]), _ptr(act[t0 * top:(t0 + n) * top]), _ptr(out[t0:t0 + n]), _i(_dt(x.dtype)), _i(n),
               _i(D), _i(F), _i(top), _stream(), kernels=2)
+    return out
+
+
+MOE_GROUPED_MIN_TOKENS = 17     # from here on bfloat16 tokens are sorted by expert and go through the library's grouped product
+
+
+def moe_grouped_fits(x: torch.Tensor, w_gate_up: torch.Tensor) -> bool:
+    """Whether a step's tokens take the sorted, grouped form (else the expert-streaming kernels do)."""
+    D, F = w_gate_up.shape[2], w_gate_up.shape[1] // 2
+    return (x.dtype == torch.bfloat16 and x.shape[0] >= MOE_GROUPED_MIN_TOKENS and D % 8 == 0 and F % 8 == 0
+            and hasattr(torch, "_grouped_mm"))
+
+
+def moe_experts_grouped(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor,
+                        weight: torch.Tensor) -> torch.Tensor:
+    """``moe_experts`` for many bfloat16 tokens: the tokens' copies are sorted by expert (a stable sort: nothing depends
+    on the order in which blocks finish), each expert's run goes through the library's grouped matrix product (32-bit
+    sums, bfloat16 results) for gate/up and for down, with the gated SiLU between them and the weighted sum of every
+    token's copies after them in kernels of this library.  No value is read on the host."""
+    _need(x, "x", torch.bfloat16, 2)
+    _need(w_gate_up, "w_gate_up", torch.bfloat16, 3)
+    _need(w_down, "w_down", torch.bfloat16, 3)
+    _need(chosen, "chosen", torch.int32, 2)
+    _need(weight, "weight", torch.float32, 2)
+    T, D = x.shape
+    E, F2, _ = w_gate_up.shape
+    F, top = F2 // 2, chosen.shape[1]
+    flat = chosen.view(-1)
+    order = torch.argsort(flat, stable=True)                        # sorted row -> copy (t * top + k)
+    ends = torch.searchsorted(flat.index_select(0, order), torch.arange(E, dtype=torch.int32, device=x.device),
+                              right=True).to(torch.int32)           # where each expert's run ends (no value read on the host)
+    place = torch.empty_like(order)
+    place[order] = torch.arange(order.numel(), device=x.device)     # copy -> sorted row
+    xs = x.index_select(0, order // top)
+    gu = torch._grouped_mm(xs, w_gate_up.transpose(1, 2), offs=ends).contiguous()
+    act = torch.empty((T * top, F), dtype=torch.bfloat16, device=x.device)
+    _call("moe", "qwb_moe_gated_act", _ptr(gu), _ptr(act), _i(T * top), _i(F), _stream())
+    y = torch._grouped_mm(act, w_down.transpose(1, 2), offs=ends).contiguous()
+    out = torch.empty((T, D), dtype=torch.float32, device=x.device)
+    _call("moe", "qwb_moe_combine", _ptr(y), _ptr(place), _ptr(weight), _ptr(out), _i(T), _i(D), _i(top), _stream())
     return out
 
 

@@ -59,6 +59,8 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x, ctx):
         chosen, weight = ops.moe_route(linear(x, self.w_router), self.top, self.renormalize)
+        if ops.moe_grouped_fits(x, self.w_gate_up):
+            return ops.moe_experts_grouped(x, self.w_gate_up, self.w_down, chosen, weight)
         return ops.moe_experts(x, self.w_gate_up, self.w_down, chosen, weight)
 
 

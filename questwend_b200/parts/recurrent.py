@@ -27,7 +27,7 @@ class Mamba2Mixer(Mixer):
     weight, and the output projection.
 
     params: hidden_size, heads, vdim, state, groups, norm_groups, conv (taps), norm_eps, names (optional overrides).
-    State per sequence: the convolution's last taps - 1 inputs [taps - 1, channels] and S [heads, state, vdim]."""
+    State per sequence: the convolution's last taps - 1 inputs [taps - 1, channels] and S, stored [heads, vdim, state]."""
 
     NAMES = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "dt_bias": "dt_bias", "A_log": "A_log", "D": "D",
              "norm": "norm", "out": "o"}
@@ -72,7 +72,7 @@ class Mamba2Mixer(Mixer):
 
     def state_spec(self):
         return (StateSpec((self.taps - 1, self.channels), torch.float32),
-                StateSpec((self.heads, self.n_state, self.vdim), torch.float32))
+                StateSpec((self.heads, self.vdim, self.n_state), torch.float32))       # column by column
 
     def forward(self, x, ctx, cache):
         tail, state = cache.state
@@ -95,7 +95,7 @@ class GatedDeltaMixer(Mixer):
     times a weight shared by the heads, times sigmoid(W_g2 W_g1 h); then the output projection.
 
     params: hidden_size, heads, key_heads, key_dim, vdim, conv (taps), decay_rank, gate_rank, norm_eps, unit_eps
-    (default 1e-6), names.  State per sequence: the convolutions' last taps - 1 inputs and S [heads, key_dim, vdim]."""
+    (default 1e-6), names.  State per sequence: the convolutions' last taps - 1 inputs and S, stored [heads, vdim, key_dim]."""
 
     NAMES = {"q": "q", "k": "k", "v": "v", "q_conv": "q.conv", "k_conv": "k.conv", "v_conv": "v.conv", "beta": "b",
              "A_log": "A_log", "decay_down": "a1", "decay_up": "a2", "dt_bias": "dt_bias", "gate_down": "g1",
@@ -148,7 +148,7 @@ class GatedDeltaMixer(Mixer):
 
     def state_spec(self):
         return (StateSpec((self.taps - 1, self.channels), torch.float32),
-                StateSpec((self.heads, self.key_dim, self.vdim), torch.float32))
+                StateSpec((self.heads, self.vdim, self.key_dim), torch.float32))       # column by column
 
     def forward(self, x, ctx, cache):
         tail, state = cache.state

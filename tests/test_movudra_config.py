@@ -74,7 +74,7 @@ def test_load_config_reads_the_shapes_of_a_folder(tmp_path):
     (("layers", 1, "mixer", "rot", "dims"), 10, "dims"), (("layers", 1, "mixer", "kv_rank"), 600, "kv_rank"),
     (("layers", 1, "mixer", "scale"), None, "scale"), (("layers", 1, "mlp", "router", "top"), 7, "top"),
     (("layers", 1, "mlp", "kind"), "sparse", "kind"), (("layers", 2, "mixer", "groups"), 4, "groups"),
-    (("layers", 2, "mixer", "norm_groups"), 5, "norm_groups"), (("layers", 2, "mixer", "state"), 70000, "state"),
+    (("layers", 2, "mixer", "norm_groups"), 5, "norm_groups"), (("layers", 2, "mixer", "state"), 513, "state"),
     (("layers", 1, "mixer", "rot", "scaling", "factor"), None, "factor")])
 def test_a_bad_value_is_refused_with_its_key(path, value, word):
     d = copy.deepcopy(mh.MIXED)
@@ -96,13 +96,13 @@ def test_the_cache_holds_one_row_per_token_and_both_states():
     model = Model(plan, Runtime(torch.device("cpu"), torch.float32))
     units = model.cache_units()
     assert units[1][0] == KVSpec(1, 48, 5, values=False) and units[3][0] == KVSpec(1, 36, 70, values=False)
-    assert units[0][1] == (StateSpec((3, 240), torch.float32), StateSpec((6, 16, 24), torch.float32))
-    assert units[5][1] == (StateSpec((0, 112), torch.float32), StateSpec((2, 16, 40), torch.float32))
+    assert units[0][1] == (StateSpec((3, 240), torch.float32), StateSpec((6, 24, 16), torch.float32))
+    assert units[5][1] == (StateSpec((0, 112), torch.float32), StateSpec((2, 40, 16), torch.float32))
     cache = CacheManager(units, 256, 3, 256, torch.float32, "cpu")
     assert cache.n_groups() == 2
     u1, u0 = cache.unit_cache(1), cache.unit_cache(0)
     assert u1.v_pool is None and tuple(u1.k_pool.shape) == (4, 1, 64, 48)
-    assert isinstance(u0.state, tuple) and tuple(u0.state[1].shape) == (3, 6, 16, 24)
+    assert isinstance(u0.state, tuple) and tuple(u0.state[1].shape) == (3, 6, 24, 16)
     a, b = cache.open(2)
     u0.state[0][b].fill_(3.0)
     u0.state[1][b].fill_(5.0)

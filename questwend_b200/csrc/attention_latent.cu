@@ -14,13 +14,16 @@
 //   c = dkv[:L] / rms(dkv[:L]) * c_weight          -> cache row [:L]
 //   rotated key part: pairs (2i, 2i + 1) of dkv[L:] -> cache row [L:]  (values beyond 2 * half pass unchanged)
 //   q_rot[t, h, :] = the same rotation of q[t, h, K:]; q_plain[h, t, :] = q[t, h, :K] in the products' dtype
+//   or, for the tensor-core prompt kernel (q_full given): q_full[t, h, :] = [q[t, h, :K] | rotated part] and
+//   row_new[t, :] = the cache row again, token by token, both in the products' dtype
 // cos, sin [T, half] already hold any factor on them.
 // ---------------------------------------------------------------------------------
 template <typename T>
 __global__ void latent_prep_kernel(const float* __restrict__ q, const float* __restrict__ dkv, const float* __restrict__ c_weight,
                                    const float* __restrict__ cosv, const float* __restrict__ sinv, const int* __restrict__ tok_seq,
                                    const int* __restrict__ tok_pos, const int* __restrict__ page_table, T* __restrict__ pool,
-                                   T* __restrict__ q_plain, float* __restrict__ q_rot, int n_tok, int H, int K, int R, int L,
+                                   T* __restrict__ q_plain, float* __restrict__ q_rot, T* __restrict__ q_full, T* __restrict__ row_new,
+                                   int n_tok, int H, int K, int R, int L,
                                    int half, float eps, int page_size, int table_width, int store) {
     pdl_wait();
     pdl_launch_dependents();
@@ -29,23 +32,41 @@ __global__ void latent_prep_kernel(const float* __restrict__ q, const float* __r
     const float* drow = dkv + (size_t)t * (L + R);
     const float* cs = cosv + (size_t)t * half;
     const float* sn = sinv + (size_t)t * half;
-    if (store) {
+    if (store || row_new) {
         float ss = 0.f;
         for (int i = threadIdx.x; i < L; i += blockDim.x) ss += drow[i] * drow[i];
         const float scale = rsqrtf(block_sum(ss, red) / (float)L + eps);
         const int b = tok_seq[t], pos = tok_pos[t];
-        T* dst = pool + ((size_t)page_table[(size_t)b * table_width + pos / page_size] * page_size + pos % page_size) * (L + R);
-        for (int i = threadIdx.x; i < L; i += blockDim.x) dst[i] = from_f32<T>(drow[i] * scale * c_weight[i]);
+        T* dst = store ? pool + ((size_t)page_table[(size_t)b * table_width + pos / page_size] * page_size + pos % page_size) * (L + R) : nullptr;
+        T* again = row_new ? row_new + (size_t)t * (L + R) : nullptr;
+        for (int i = threadIdx.x; i < L; i += blockDim.x) {
+            const T c = from_f32<T>(drow[i] * scale * c_weight[i]);
+            if (dst) dst[i] = c;
+            if (again) again[i] = c;
+        }
         for (int i = threadIdx.x; i < R; i += blockDim.x) {
             float v = drow[L + i];
             if (i < 2 * half) {
                 const float other = drow[L + (i ^ 1)], c = cs[i >> 1], s = sn[i >> 1];
                 v = (i & 1) ? v * c + other * s : v * c - other * s;
             }
-            dst[L + i] = from_f32<T>(v);
+            if (dst) dst[L + i] = from_f32<T>(v);
+            if (again) again[L + i] = from_f32<T>(v);
         }
     }
     const float* qrow = q + (size_t)t * H * (K + R);
+    if (q_full) {
+        for (int idx = threadIdx.x; idx < H * (K + R); idx += blockDim.x) {
+            const int h = idx / (K + R), i = idx - h * (K + R) - K;       // i >= 0: the rotated part
+            float v = qrow[idx];
+            if (i >= 0 && i < 2 * half) {
+                const float other = qrow[h * (K + R) + K + (i ^ 1)], c = cs[i >> 1], s = sn[i >> 1];
+                v = (i & 1) ? v * c + other * s : v * c - other * s;
+            }
+            q_full[(size_t)t * H * (K + R) + idx] = from_f32<T>(v);
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < H * K; idx += blockDim.x) {
         const int h = idx / K, d = idx - h * K;
         q_plain[((size_t)h * n_tok + t) * K + d] = from_f32<T>(qrow[h * (K + R) + d]);
@@ -64,17 +85,19 @@ __global__ void latent_prep_kernel(const float* __restrict__ q, const float* __r
 
 extern "C" int qwb_latent_prep(const float* q, const float* dkv, const float* c_weight, const float* cosv, const float* sinv,
                                const int* tok_seq, const int* tok_pos, const int* page_table, void* pool, int dtype,
-                               void* q_plain, float* q_rot, int T, int H, int K, int R, int L, int half, float eps,
-                               int page_size, int table_width, int store, cudaStream_t stream) {
+                               void* q_plain, float* q_rot, void* q_full, void* row_new, int T, int H, int K, int R, int L,
+                               int half, float eps, int page_size, int table_width, int store, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || K <= 0 || R < 0 || L <= 0 || half < 0 || 2 * half > R)
         return qwb_fail(QWB_ERR_ARG, "latent_prep: %d heads of %d + %d, latent %d, %d rotated pairs", H, K, R, L, half);
     if (dtype == QWB_DT_F32)
         qwb_launch(latent_prep_kernel<float>, T, 128, 0, stream, q, dkv, c_weight, cosv, sinv, tok_seq, tok_pos, page_table,
-                   (float*)pool, (float*)q_plain, q_rot, T, H, K, R, L, half, eps, page_size, table_width, store);
+                   (float*)pool, (float*)q_plain, q_rot, (float*)q_full, (float*)row_new, T, H, K, R, L, half, eps, page_size,
+                   table_width, store);
     else if (dtype == QWB_DT_BF16)
         qwb_launch(latent_prep_kernel<bf16>, T, 128, 0, stream, q, dkv, c_weight, cosv, sinv, tok_seq, tok_pos, page_table,
-                   (bf16*)pool, (bf16*)q_plain, q_rot, T, H, K, R, L, half, eps, page_size, table_width, store);
+                   (bf16*)pool, (bf16*)q_plain, q_rot, (bf16*)q_full, (bf16*)row_new, T, H, K, R, L, half, eps, page_size,
+                   table_width, store);
     else
         return qwb_fail(QWB_ERR_ARG, "latent_prep: unknown dtype %d", dtype);
     return qwb_check_launch("latent_prep");

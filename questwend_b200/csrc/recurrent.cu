@@ -75,9 +75,10 @@ extern "C" int qwb_short_conv(const float* x, int ld, const float* w, const floa
 // The recurrences keep, per head, a state matrix S of rows x P (state or key size x value size) whose columns never
 // meet: column p is read and written with the token's value p only.  So one WARP owns one column: lane l keeps rows
 // l * PER .. l * PER + PER - 1 in registers, a sum over the rows is a shuffle reduction, and there is no shared
-// memory and no barrier; a block is four columns of one head, the grid (columns / 4, heads, sequences).  The state
-// is stored column by column, [slots, H, P, rows], so that a warp's piece is one contiguous run.  A token's vectors
-// are asked for one token ahead.
+// memory and no barrier (a warp takes 2 or 4 columns where few rows fall to a lane: they share the loads of a
+// token's vectors); a block is four warps of one head, the grid (warps' columns / 4, heads, sequences).  The state
+// is stored column by column, [slots, H, P, rows], so that a warp's piece is one contiguous run.  The vectors of a
+// few tokens are asked for together.
 // ---------------------------------------------------------------------------------
 #define QWB_SCAN_WARPS 4
 #define QWB_SCAN_MAX_PER 16
@@ -98,11 +99,20 @@ __device__ __forceinline__ void load_rows(const float* __restrict__ base, int n0
     }
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+#define QWB_SCAN_AHEAD 8        // rounds of tokens whose vectors are asked into L2 ahead of their use
+#ifndef QWB_SSM_CW_MAX
+#define QWB_SSM_CW_MAX 4        // the most columns a warp takes in the Mamba-2 recurrence ...
+#endif
+#ifndef QWB_DELTA_CW_MAX
+#define QWB_DELTA_CW_MAX 2      // ... and in the delta rule (a token's two sums over the rows sit in its chain: 2 measured best)
+#endif
+
 // Mamba-2.  Per head h (group g = h / (H / G)), per token:
 //     dt = softplus(dt_raw + dt_bias[h]);  S = exp(-exp(A_log[h]) dt) S + dt B x^T;  y = S^T C + D[h] x
 //   xbc [T, ldx] float: x [H * P] | B [G * N] | C [G * N] (after convolution and SiLU)
 //   dt_raw: column h of a [T, ld_dt] matrix;  state [slots, H, P, N];  y [T, H * P]
-template <int PER, bool VEC>
+template <int PER, bool VEC, int TB, int CW>
 __global__ void __launch_bounds__(32 * QWB_SCAN_WARPS)
 ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const float* __restrict__ dt_raw, int ld_dt,
                 const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dskip,
@@ -111,52 +121,89 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const float* __restrict_
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
-    const int p = blockIdx.x * QWB_SCAN_WARPS + (threadIdx.x >> 5), h = blockIdx.y, b = blockIdx.z;
-    if (p >= P) return;
+    const int p0 = (blockIdx.x * QWB_SCAN_WARPS + (threadIdx.x >> 5)) * CW, h = blockIdx.y, b = blockIdx.z;
+    if (p0 >= P) return;                                            // P is a multiple of CW: a warp's columns all exist
     const int g = h / (H / G);
     const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
     const int n0 = lane * PER;
-    float* S = state + (((size_t)slots[b] * H + h) * P + p) * N;
-    float s[PER];
-    load_rows<PER, VEC>(S, n0, N, s);
+    float* S = state + (((size_t)slots[b] * H + h) * P + p0) * N;
+    float s[CW][PER];
+#pragma unroll
+    for (int c = 0; c < CW; ++c) load_rows<PER, VEC>(S + (size_t)c * N, n0, N, s[c]);
     const float a = -expf(A_log[h]), dskip = Dskip[h], bias = dt_bias[h];
     const int inner = H * P;
-    float Bn[PER], Cn[PER], dt_n = 0.f, x_n = 0.f;
-    if (t0 < t1) {
-        const float* row = xbc + (size_t)t0 * ldx;
-        load_rows<PER, VEC>(row + inner + g * N, n0, N, Bn);
-        load_rows<PER, VEC>(row + inner + (G + g) * N, n0, N, Cn);
-        dt_n = dt_raw[(size_t)t0 * ld_dt + h];
-        x_n = row[h * P + p];
-    }
-    for (int t = t0; t < t1; ++t) {
-        float Bt[PER], Ct[PER];
+    // TB tokens a round: their vectors are asked for together (once for the warp's CW columns) and a round ahead of
+    // their use (and into L2 some rounds earlier: a prompt's rows come from HBM once, in the order of the tokens); the
+    // state runs through a round's tokens in order, and the sums over the rows are reduced side by side
+    float Bn[TB][PER], Cn[TB][PER], dt_n[TB], x_n[TB][CW];
+    auto load_round = [&](int tc) {
 #pragma unroll
-        for (int k = 0; k < PER; ++k) { Bt[k] = Bn[k]; Ct[k] = Cn[k]; }
-        const float dt_in = dt_n, xv = x_n;
-        if (t + 1 < t1) {
-            const float* row = xbc + (size_t)(t + 1) * ldx;
-            load_rows<PER, VEC>(row + inner + g * N, n0, N, Bn);
-            load_rows<PER, VEC>(row + inner + (G + g) * N, n0, N, Cn);
-            dt_n = dt_raw[(size_t)(t + 1) * ld_dt + h];
-            x_n = row[h * P + p];
-        }
-        const float dt = softplus_f(dt_in + bias);
-        const float decay = expf(a * dt);
-        const float dtx = dt * xv;
-        float acc = 0.f;
+        for (int j = 0; j < TB; ++j) {
+            const int t = min(tc + j, t1 - 1);                      // past the end: the last token again, not used
+            const float* row = xbc + (size_t)t * ldx;
+            load_rows<PER, VEC>(row + inner + g * N, n0, N, Bn[j]);
+            load_rows<PER, VEC>(row + inner + (G + g) * N, n0, N, Cn[j]);
+            dt_n[j] = dt_raw[(size_t)t * ld_dt + h];
 #pragma unroll
-        for (int k = 0; k < PER; ++k) {
-            s[k] = decay * s[k] + dtx * Bt[k];
-            acc += s[k] * Ct[k];
+            for (int c = 0; c < CW; ++c) x_n[j][c] = row[h * P + p0 + c];
         }
-        acc = warp_sum(acc);
-        if (lane == 0) y[(size_t)t * inner + h * P + p] = acc + dskip * xv;
+    };
+    if (t0 < t1) load_round(t0);
+    for (int tc = t0; tc < t1; tc += TB) {
+        float Bt[TB][PER], Ct[TB][PER], dt_in[TB], xv[TB][CW];
+#pragma unroll
+        for (int j = 0; j < TB; ++j) {
+            dt_in[j] = dt_n[j];
+#pragma unroll
+            for (int k = 0; k < PER; ++k) { Bt[j][k] = Bn[j][k]; Ct[j][k] = Cn[j][k]; }
+#pragma unroll
+            for (int c = 0; c < CW; ++c) xv[j][c] = x_n[j][c];
+        }
+        if (tc + TB < t1) load_round(tc + TB);
+#pragma unroll
+        for (int j = 0; j < TB; ++j) {
+            const int t = tc + QWB_SCAN_AHEAD * TB + j;
+            if (t < t1 && n0 < N) {
+                const float* row = xbc + (size_t)t * ldx + inner + g * N + n0;
+                prefetch_l2(row);
+                prefetch_l2(row + G * N);
+                if (lane == 0) prefetch_l2(xbc + (size_t)t * ldx + h * P + p0);
+            }
+        }
+        float acc[TB][CW];
+#pragma unroll
+        for (int j = 0; j < TB; ++j) {
+            const float dt = softplus_f(dt_in[j] + bias);
+            const float decay = expf(a * dt);
+#pragma unroll
+            for (int c = 0; c < CW; ++c) {
+                acc[j][c] = 0.f;
+                if (tc + j < t1) {
+                    const float dtx = dt * xv[j][c];
+#pragma unroll
+                    for (int k = 0; k < PER; ++k) {
+                        s[c][k] = decay * s[c][k] + dtx * Bt[j][k];
+                        acc[j][c] += s[c][k] * Ct[j][k];
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < TB; ++j)
+#pragma unroll
+            for (int c = 0; c < CW; ++c) acc[j][c] = warp_sum(acc[j][c]);
+#pragma unroll
+        for (int j = 0; j < TB; ++j)
+#pragma unroll
+            for (int c = 0; c < CW; ++c)
+                if (lane == 0 && tc + j < t1) y[(size_t)(tc + j) * inner + h * P + p0 + c] = acc[j][c] + dskip * xv[j][c];
     }
     if (write_state) {
 #pragma unroll
-        for (int k = 0; k < PER; ++k)
-            if (n0 + k < N) S[n0 + k] = s[k];
+        for (int c = 0; c < CW; ++c)
+#pragma unroll
+            for (int k = 0; k < PER; ++k)
+                if (n0 + k < N) S[(size_t)c * N + n0 + k] = s[c][k];
     }
 }
 
@@ -175,13 +222,18 @@ extern "C" int qwb_ssm_scan(const float* xbc, int ldx, const float* dt_raw, int 
     const int per = scan_rows_per_lane(N);
     if (!per) return qwb_fail(QWB_ERR_ARG, "ssm_scan: a state of %d rows per head is too large (up to %d)", N, 32 * QWB_SCAN_MAX_PER);
     if (B > 65535 || H > 65535) return qwb_fail(QWB_ERR_ARG, "ssm_scan: %d sequences or %d heads are too many", B, H);
-    const dim3 grid((P + QWB_SCAN_WARPS - 1) / QWB_SCAN_WARPS, H, B);
     const bool vec = per >= 4 && N % 4 == 0 && ldx % 4 == 0 && (H * P) % 4 == 0 && aligned16(xbc) && aligned16(state);
-#define QWB_SSM(PER, VEC) qwb_launch(ssm_scan_kernel<PER, VEC>, grid, 32 * QWB_SCAN_WARPS, 0, stream, xbc, ldx, dt_raw, ld_dt, dt_bias, A_log, Dskip, state, cu_seqlens, slots, y, H, P, N, G, write_state)
+    // columns a warp: 4 or 2 where the rows a lane keeps are few and the value size divides; the columns share the loads
+    int cw = per <= 4 && P % 4 == 0 ? 4 : (per <= 8 && P % 2 == 0 ? 2 : 1);
+    if (cw > QWB_SSM_CW_MAX) cw = QWB_SSM_CW_MAX;
+    const dim3 grid((P / cw + QWB_SCAN_WARPS - 1) / QWB_SCAN_WARPS, H, B);
+#define QWB_SSM1(PER, VEC, CW) qwb_launch(ssm_scan_kernel<PER, VEC, (PER <= 4 ? 4 : (PER == 8 ? 2 : 1)), CW>, grid, 32 * QWB_SCAN_WARPS, 0, stream, xbc, ldx, dt_raw, ld_dt, dt_bias, A_log, Dskip, state, cu_seqlens, slots, y, H, P, N, G, write_state)
+#define QWB_SSM(PER, VEC) do { if (cw == 4 && PER <= 4) QWB_SSM1(PER, VEC, (PER <= 4 ? 4 : 1)); else if (cw >= 2 && PER <= 8) QWB_SSM1(PER, VEC, (PER <= 8 ? 2 : 1)); else QWB_SSM1(PER, VEC, 1); } while (0)
     if (per == 1) QWB_SSM(1, false); else if (per == 2) QWB_SSM(2, false);
     else if (per == 4) { if (vec) QWB_SSM(4, true); else QWB_SSM(4, false); }
     else if (per == 8) { if (vec) QWB_SSM(8, true); else QWB_SSM(8, false); }
     else { if (vec) QWB_SSM(16, true); else QWB_SSM(16, false); }
+#undef QWB_SSM1
 #undef QWB_SSM
     return qwb_check_launch("ssm_scan");
 }
@@ -235,7 +287,7 @@ extern "C" int qwb_delta_prep(float* qkv, int ld, float* kq, const float* b_raw,
 //     S = decay[:, None] * S;  u = beta (v - S^T k);  S = S + k u^T;  o = S^T q
 // o is formed as (decayed S)^T q + u (k . q), so that both sums over the rows are taken in one pass.  A warp per
 // column, as above; state [slots, H, P, K].
-template <int PER, bool VEC>
+template <int PER, bool VEC, int TB, int CW>
 __global__ void __launch_bounds__(32 * QWB_SCAN_WARPS)
 delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ kq, const float* __restrict__ beta,
                   const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ cu_seqlens,
@@ -243,53 +295,88 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
-    const int p = blockIdx.x * QWB_SCAN_WARPS + (threadIdx.x >> 5), h = blockIdx.y, b = blockIdx.z;
-    if (p >= P) return;
+    const int p0 = (blockIdx.x * QWB_SCAN_WARPS + (threadIdx.x >> 5)) * CW, h = blockIdx.y, b = blockIdx.z;
+    if (p0 >= P) return;                                            // P is a multiple of CW: a warp's columns all exist
     const int kh = h / (H / Hk);
     const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
     const int n0 = lane * PER;
-    float* S = state + (((size_t)slots[b] * H + h) * P + p) * K;
-    float s[PER];
-    load_rows<PER, VEC>(S, n0, K, s);
-    const int v_at = 2 * Hk * K + h * P + p;
-    float kn[PER], qn[PER], gn[PER], v_n = 0.f, beta_n = 0.f, kq_n = 0.f;
-    if (t0 < t1) {
-        const float* row = qkv + (size_t)t0 * ld;
-        load_rows<PER, VEC>(row + kh * K, n0, K, qn);
-        load_rows<PER, VEC>(row + (Hk + kh) * K, n0, K, kn);
-        load_rows<PER, VEC>(decay + ((size_t)t0 * H + h) * K, n0, K, gn);
-        v_n = row[v_at]; beta_n = beta[(size_t)t0 * H + h]; kq_n = kq[(size_t)t0 * Hk + kh];
-    }
-    for (int t = t0; t < t1; ++t) {
-        float kk[PER], qq[PER], gg[PER];
+    float* S = state + (((size_t)slots[b] * H + h) * P + p0) * K;
+    float s[CW][PER];
 #pragma unroll
-        for (int k = 0; k < PER; ++k) { kk[k] = kn[k]; qq[k] = qn[k]; gg[k] = gn[k]; }
-        const float v = v_n, bt = beta_n, kqv = kq_n;
-        if (t + 1 < t1) {
-            const float* row = qkv + (size_t)(t + 1) * ld;
-            load_rows<PER, VEC>(row + kh * K, n0, K, qn);
-            load_rows<PER, VEC>(row + (Hk + kh) * K, n0, K, kn);
-            load_rows<PER, VEC>(decay + ((size_t)(t + 1) * H + h) * K, n0, K, gn);
-            v_n = row[v_at]; beta_n = beta[(size_t)(t + 1) * H + h]; kq_n = kq[(size_t)(t + 1) * Hk + kh];
+    for (int c = 0; c < CW; ++c) load_rows<PER, VEC>(S + (size_t)c * K, n0, K, s[c]);
+    const int v_at = 2 * Hk * K + h * P + p0;
+    // TB tokens a round: their vectors are asked for together (once for the warp's CW columns) and a round ahead of
+    // their use (and into L2 some rounds earlier); the state then runs through a round's tokens in order (a token's
+    // write needs the sum over the rows of the token before it), the columns side by side
+    float kn[TB][PER], qn[TB][PER], gn[TB][PER], v_n[TB][CW], bt_n[TB], kq_n[TB];
+    auto load_round = [&](int tc) {
+#pragma unroll
+        for (int j = 0; j < TB; ++j) {
+            const int t = min(tc + j, t1 - 1);                      // past the end: the last token again, not used
+            const float* row = qkv + (size_t)t * ld;
+            load_rows<PER, VEC>(row + kh * K, n0, K, qn[j]);
+            load_rows<PER, VEC>(row + (Hk + kh) * K, n0, K, kn[j]);
+            load_rows<PER, VEC>(decay + ((size_t)t * H + h) * K, n0, K, gn[j]);
+#pragma unroll
+            for (int c = 0; c < CW; ++c) v_n[j][c] = row[v_at + c];
+            bt_n[j] = beta[(size_t)t * H + h]; kq_n[j] = kq[(size_t)t * Hk + kh];
         }
-        float sk = 0.f, sq = 0.f;
+    };
+    if (t0 < t1) load_round(t0);
+    for (int tc = t0; tc < t1; tc += TB) {
+        float kk[TB][PER], qq[TB][PER], gg[TB][PER], v[TB][CW], bt[TB], kqv[TB];
 #pragma unroll
-        for (int k = 0; k < PER; ++k) {
-            s[k] *= gg[k];
-            sk += s[k] * kk[k];
-            sq += s[k] * qq[k];
+        for (int j = 0; j < TB; ++j) {
+            bt[j] = bt_n[j]; kqv[j] = kq_n[j];
+#pragma unroll
+            for (int k = 0; k < PER; ++k) { kk[j][k] = kn[j][k]; qq[j][k] = qn[j][k]; gg[j][k] = gn[j][k]; }
+#pragma unroll
+            for (int c = 0; c < CW; ++c) v[j][c] = v_n[j][c];
         }
-        sk = warp_sum(sk);
-        sq = warp_sum(sq);
-        const float u = bt * (v - sk);
+        if (tc + TB < t1) load_round(tc + TB);
 #pragma unroll
-        for (int k = 0; k < PER; ++k) s[k] += kk[k] * u;
-        if (lane == 0) o[((size_t)t * H + h) * P + p] = sq + u * kqv;
+        for (int j = 0; j < TB; ++j) {
+            const int t = tc + QWB_SCAN_AHEAD * TB + j;
+            if (t < t1 && n0 < K) {
+                const float* row = qkv + (size_t)t * ld;
+                prefetch_l2(row + kh * K + n0);
+                prefetch_l2(row + (Hk + kh) * K + n0);
+                prefetch_l2(decay + ((size_t)t * H + h) * K + n0);
+                if (lane == 0) prefetch_l2(row + v_at);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < TB; ++j) {
+            if (tc + j < t1) {
+                float sk[CW], sq[CW];
+#pragma unroll
+                for (int c = 0; c < CW; ++c) {
+                    sk[c] = sq[c] = 0.f;
+#pragma unroll
+                    for (int k = 0; k < PER; ++k) {
+                        s[c][k] *= gg[j][k];
+                        sk[c] += s[c][k] * kk[j][k];
+                        sq[c] += s[c][k] * qq[j][k];
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < CW; ++c) { sk[c] = warp_sum(sk[c]); sq[c] = warp_sum(sq[c]); }
+#pragma unroll
+                for (int c = 0; c < CW; ++c) {
+                    const float u = bt[j] * (v[j][c] - sk[c]);
+#pragma unroll
+                    for (int k = 0; k < PER; ++k) s[c][k] += kk[j][k] * u;
+                    if (lane == 0) o[((size_t)(tc + j) * H + h) * P + p0 + c] = sq[c] + u * kqv[j];
+                }
+            }
+        }
     }
     if (write_state) {
 #pragma unroll
-        for (int k = 0; k < PER; ++k)
-            if (n0 + k < K) S[n0 + k] = s[k];
+        for (int c = 0; c < CW; ++c)
+#pragma unroll
+            for (int k = 0; k < PER; ++k)
+                if (n0 + k < K) S[(size_t)c * K + n0 + k] = s[c][k];
     }
 }
 
@@ -301,13 +388,17 @@ extern "C" int qwb_delta_scan(const float* qkv, int ld, const float* kq, const f
     const int per = scan_rows_per_lane(K);
     if (!per) return qwb_fail(QWB_ERR_ARG, "delta_scan: a state of %d rows per head is too large (up to %d)", K, 32 * QWB_SCAN_MAX_PER);
     if (B > 65535 || H > 65535) return qwb_fail(QWB_ERR_ARG, "delta_scan: %d sequences or %d heads are too many", B, H);
-    const dim3 grid((P + QWB_SCAN_WARPS - 1) / QWB_SCAN_WARPS, H, B);
     const bool vec = per >= 4 && K % 4 == 0 && ld % 4 == 0 && aligned16(qkv) && aligned16(decay) && aligned16(state);
-#define QWB_DELTA(PER, VEC) qwb_launch(delta_scan_kernel<PER, VEC>, grid, 32 * QWB_SCAN_WARPS, 0, stream, qkv, ld, kq, beta, decay, state, cu_seqlens, slots, o, H, Hk, K, P, write_state)
+    int cw = per <= 4 && P % 4 == 0 ? 4 : (per <= 8 && P % 2 == 0 ? 2 : 1);            // columns a warp, as in ssm_scan
+    if (cw > QWB_DELTA_CW_MAX) cw = QWB_DELTA_CW_MAX;
+    const dim3 grid((P / cw + QWB_SCAN_WARPS - 1) / QWB_SCAN_WARPS, H, B);
+#define QWB_DELTA1(PER, VEC, CW) qwb_launch(delta_scan_kernel<PER, VEC, (PER <= 4 ? 4 : (PER == 8 ? 2 : 1)), CW>, grid, 32 * QWB_SCAN_WARPS, 0, stream, qkv, ld, kq, beta, decay, state, cu_seqlens, slots, o, H, Hk, K, P, write_state)
+#define QWB_DELTA(PER, VEC) do { if (cw == 4 && PER <= 4) QWB_DELTA1(PER, VEC, (PER <= 4 ? 4 : 1)); else if (cw >= 2 && PER <= 8) QWB_DELTA1(PER, VEC, (PER <= 8 ? 2 : 1)); else QWB_DELTA1(PER, VEC, 1); } while (0)
     if (per == 1) QWB_DELTA(1, false); else if (per == 2) QWB_DELTA(2, false);
     else if (per == 4) { if (vec) QWB_DELTA(4, true); else QWB_DELTA(4, false); }
     else if (per == 8) { if (vec) QWB_DELTA(8, true); else QWB_DELTA(8, false); }
     else { if (vec) QWB_DELTA(16, true); else QWB_DELTA(16, false); }
+#undef QWB_DELTA1
 #undef QWB_DELTA
     return qwb_check_launch("delta_scan");
 }

@@ -112,7 +112,7 @@ def build_step_context(cache: CacheManager, entries: list, vocab_size: int, devi
     ctx = StepContext(n_tokens=T, n_seqs=B, token_ids=parts[0], tok_seq=parts[1], tok_pos=parts[2],
                       cu_seqlens=parts[3], pos0=parts[4], seq_len=parts[5], slots=parts[6],
                       max_new=max(n_new), max_len=int(max(slen)), single_token=all(n == 1 for n in n_new),
-                      page_tables=tables, host_slots=slots)
+                      page_tables=tables, host_slots=slots, all_start=all(p == 0 for p in pos0))
     return ctx, parts[7]
 
 

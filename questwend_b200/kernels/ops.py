@@ -780,11 +780,13 @@ LATENT_RUN_KEYS = 64        # ... QWB_LATENT_RUN_KEYS: keys per block in a step 
 
 
 def latent_prep(q: torch.Tensor, dkv: torch.Tensor, c_weight: torch.Tensor, cos, sin, ctx, page_table, pool,
-                heads: int, dim: int, rot_dim: int, rank: int, eps: float, store: bool = True):
+                heads: int, dim: int, rot_dim: int, rank: int, eps: float, store: bool = True, whole_heads: bool = False):
     """Per token: the latent (``dkv[:, :rank]``, RMS-normed, times ``c_weight``) and the rotated shared key part
     (``dkv[:, rank:]``, pairs (2i, 2i + 1) turned by cos/sin [T, half]) go into the cache row of the token's position;
     each head's rotated query part is turned the same way.  ``q`` float32 [T, heads * (dim + rot_dim)].
-    Returns (q_plain [heads, T, dim] in the pool's dtype, q_rot float32 [T, heads, rot_dim])."""
+    Returns (q_plain [heads, T, dim] in the pool's dtype, q_rot float32 [T, heads, rot_dim]); or, with ``whole_heads``
+    (for the tensor-core prompt kernel), (q [T, heads, dim + rot_dim] with the rotated parts turned, the tokens' cache
+    rows once more as [T, rank + rot_dim]), both in the pool's dtype."""
     _need(q, "q", torch.float32, 2)
     _need(dkv, "dkv", torch.float32, 2)
     _need(c_weight, "c_weight", torch.float32, 1)
@@ -802,13 +804,46 @@ def latent_prep(q: torch.Tensor, dkv: torch.Tensor, c_weight: torch.Tensor, cos,
             or pool.shape[1] != 1 or pool.shape[3] != rank + rot_dim):
         raise KernelError(f"latent_prep: q {tuple(q.shape)}, dkv {tuple(dkv.shape)}, pool {tuple(pool.shape)} do not fit "
                           f"{heads} heads of {dim} + {rot_dim}, latent {rank}")
-    q_plain = torch.empty((heads, T, dim), dtype=pool.dtype, device=q.device)
-    q_rot = torch.empty((T, heads, rot_dim), dtype=torch.float32, device=q.device)
+    q_plain = q_rot = q_full = row_new = None
+    if whole_heads:
+        q_full = torch.empty((T, heads, dim + rot_dim), dtype=pool.dtype, device=q.device)
+        row_new = torch.empty((T, rank + rot_dim), dtype=pool.dtype, device=q.device)
+    else:
+        q_plain = torch.empty((heads, T, dim), dtype=pool.dtype, device=q.device)
+        q_rot = torch.empty((T, heads, rot_dim), dtype=torch.float32, device=q.device)
     _call("attention_latent", "qwb_latent_prep", _ptr(q), _ptr(dkv), _ptr(c_weight), _ptr(cos), _ptr(sin), _ptr(ctx.tok_seq),
-          _ptr(ctx.tok_pos), _ptr(page_table), _ptr(pool), _i(_dt(pool.dtype)), _ptr(q_plain), _ptr(q_rot), _i(T), _i(heads),
-          _i(dim), _i(rot_dim), _i(rank), _i(half), _f(eps), _i(pool.shape[2]), _i(page_table.shape[1]),
-          _i(1 if store else 0), _stream())
-    return q_plain, q_rot
+          _ptr(ctx.tok_pos), _ptr(page_table), _ptr(pool), _i(_dt(pool.dtype)), _ptr(q_plain), _ptr(q_rot), _ptr(q_full),
+          _ptr(row_new), _i(T), _i(heads), _i(dim), _i(rot_dim), _i(rank), _i(half), _f(eps), _i(pool.shape[2]),
+          _i(page_table.shape[1]), _i(1 if store else 0), _stream())
+    return (q_full, row_new) if whole_heads else (q_plain, q_rot)
+
+
+def latent_prefill_fits(dtype: torch.dtype, dim: int, rot_dim: int, vdim: int, rank: int) -> bool:
+    """Whether the tensor-core prompt kernel takes these head sizes (else the plain kernel does)."""
+    return (dtype == torch.bfloat16 and dim % 8 == 0 and rot_dim % 8 == 0 and vdim % 8 == 0 and (dim + rot_dim) % 16 == 0
+            and vdim <= 256 and rank % 8 == 0 and dim + rot_dim <= 512)
+
+
+def latent_prefill(q: torch.Tensor, k_plain: torch.Tensor, rows: torch.Tensor, v: torch.Tensor, ctx, sink, scale: float,
+                   window: int, heads: int, dim: int, rot_dim: int, vdim: int) -> torch.Tensor:
+    """Attention of prompts that START their sequences (every position 0 is in this step), on the tensor cores.
+    bfloat16: ``q`` [T, heads, dim + rot_dim]; ``k_plain`` [T, heads * dim] and ``v`` [T, heads * vdim], the keys' unrotated
+    parts and the values made from the latents; ``rows`` [T, rank + rot_dim], whose last ``rot_dim`` values are the
+    rotated key part that the heads share.  Returns [T, heads * vdim]."""
+    for name, t in (("q", q), ("k_plain", k_plain), ("rows", rows), ("v", v)):
+        _need(t, name, torch.bfloat16)
+    T = q.shape[0]
+    if (tuple(q.shape) != (T, heads, dim + rot_dim) or tuple(k_plain.shape) != (T, heads * dim) or tuple(v.shape) != (T, heads * vdim)
+            or rows.shape[0] != T or rows.shape[1] < rot_dim):
+        raise KernelError(f"latent_prefill: q {tuple(q.shape)}, k {tuple(k_plain.shape)}, rows {tuple(rows.shape)}, v {tuple(v.shape)}")
+    if sink is not None:
+        _need(sink, "sink", torch.float32, 1)
+    out = torch.empty((T, heads * vdim), dtype=torch.bfloat16, device=q.device)
+    ld = rows.shape[1]
+    _call("attention_latent_mma", "qwb_latent_prefill_mma", _ptr(q), _ptr(k_plain),
+          ctypes.c_void_p(rows.data_ptr() + 2 * (ld - rot_dim)), _i(ld), _ptr(v), _ptr(ctx.cu_seqlens), _ptr(sink), _ptr(out),
+          _i(ctx.n_seqs), _i(ctx.max_new), _i(heads), _i(dim), _i(rot_dim), _i(vdim), _f(scale), _i(window), _stream())
+    return out
 
 
 def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, pool: torch.Tensor, page_table, ctx, sink, scale: float,

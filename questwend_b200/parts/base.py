@@ -78,6 +78,7 @@ class StepContext:
     host_slots: list | None     # the slots again, as Python ints; None in a step that may be replayed from a CUDA graph
                                 # (generation's single-token steps): a part that runs there reads no value on the host
     shared: dict = field(default_factory=dict)   # per-step values shared between layers (rotation tables)
+    all_start: bool = False     # every sequence of the step starts at its position 0 (whole prompts): known on the host
 
 
 class UnitCache:

@@ -16,6 +16,10 @@ from .linear import _check_true_fp32, kernel_modules as linear_modules, linear
 from .registry import register_mixer
 
 
+PROMPT_KERNEL_MIN_TOKENS = 17      # whole prompts of at least this many tokens (the longest of the step) take the
+                                   # tensor-core kernel; shorter ones are scored against the latents like single tokens
+
+
 class LatentAttention(Mixer):
     """params: hidden_size, heads, dim (unrotated query/key size per head), rot_dim (rotated size), vdim, kv_rank,
     q_rank, scale, window (0: none), sink (bool), norm_eps, names (optional overrides).
@@ -65,12 +69,16 @@ class LatentAttention(Mixer):
         self.w_q_down, self.w_q_up, self.w_kv_down, self.w_out = (weights[px + n[k]] for k in ("q_down", "q_up", "kv_down", "out"))
         self.q_norm_w = weights[px + n["q_norm"]].to(torch.float32).contiguous()
         self.kv_norm_w = weights[px + n["kv_norm"]].to(torch.float32).contiguous()
+        self.w_k_up_flat, self.w_v_up_flat = weights[px + n["k_up"]], weights[px + n["v_up"]]
         self.w_k_up = weights[px + n["k_up"]].view(H, self.dim, self.kv_rank)                    # q_plain @ this: W_uk^T q
         self.w_v_up_t = weights[px + n["v_up"]].view(H, self.vdim, self.kv_rank).transpose(1, 2)   # latent @ this: W_uv c
         self.sink = weights[px + n["sink"]].to(torch.float32).contiguous() if self.has_sink else None
 
     def kernel_modules(self):
-        return ("attention_latent", "elementwise", "rope_kv", *linear_modules(self.runtime.dtype))
+        mods = ["attention_latent", "elementwise", "rope_kv", *linear_modules(self.runtime.dtype)]
+        if ops.latent_prefill_fits(self.runtime.dtype, self.dim, self.rot_dim, self.vdim, self.kv_rank):
+            mods.append("attention_latent_mma")
+        return tuple(mods)
 
     def kv_spec(self):
         return KVSpec(1, self.kv_rank + self.rot_dim, self.window, values=False)
@@ -91,6 +99,16 @@ class LatentAttention(Mixer):
         if self.position is not None:
             cos, sin = self.position.prepare(ctx)
         table = ctx.page_tables[cache.group_id]
+        if (ctx.all_start and ctx.max_new >= PROMPT_KERNEL_MIN_TOKENS
+                and ops.latent_prefill_fits(dtype, self.dim, self.rot_dim, self.vdim, self.kv_rank)):
+            # whole prompts: keys and values per head from the prompt's own latents (two library products with bfloat16
+            # results), then the usual attention on the tensor cores
+            q_heads, rows = ops.latent_prep(q, dkv, self.kv_norm_w, cos, sin, ctx, table, cache.k_pool, H, self.dim,
+                                            self.rot_dim, self.kv_rank, self.eps, store=cache.writable, whole_heads=True)
+            c = rows[:, :self.kv_rank]
+            att = ops.latent_prefill(q_heads, torch.mm(c, self.w_k_up_flat.t()), rows, torch.mm(c, self.w_v_up_flat.t()), ctx,
+                                     self.sink, self.scale, self.window, H, self.dim, self.rot_dim, self.vdim)
+            return linear(att, self.w_out)
         q_plain, q_rot = ops.latent_prep(q, dkv, self.kv_norm_w, cos, sin, ctx, table, cache.k_pool, H, self.dim,
                                          self.rot_dim, self.kv_rank, self.eps, store=cache.writable)
         q_abs = self._per_head(q_plain, self.w_k_up)

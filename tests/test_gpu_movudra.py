@@ -106,6 +106,30 @@ def test_latent_attention_alone(entry, dtype):
         assert close(g, r, dtype)
 
 
+@pytest.mark.parametrize("window", [0, 1, 2, 63, 64, 65, 100])
+@pytest.mark.parametrize("sizes", [dict(heads=3, dim=24, rot_dim=8, vdim=40, kv_rank=40), dict(heads=2, dim=64, rot_dim=16, vdim=64, kv_rank=48),
+                                   dict(heads=1, dim=8, rot_dim=8, vdim=8, kv_rank=8, q_rank=8)])
+def test_whole_prompts_on_the_tensor_cores(sizes, window, monkeypatch):
+    """bfloat16 prompts that start their sequences take the tensor-core kernel (keys and values per head made from the
+    latents): against the plain implementation, and against the kernel that scores the latents themselves, for windows
+    around the key tile of 64 and prompts that cross two tiles, end inside one, or are a single token."""
+    from questwend_b200.kernels import ops
+    from questwend_b200.parts import latent_attention as la
+    entry = mh.latent(window=window, **sizes)
+    assert ops.latent_prefill_fits(torch.bfloat16, sizes["dim"], sizes["rot_dim"], sizes["vdim"], sizes["kv_rank"])
+    calls = []
+    kernel = ops.latent_prefill
+    monkeypatch.setattr(ops, "latent_prefill", lambda *a, **k: calls.append(1) or kernel(*a, **k))
+    got, refs = mixer_alone(entry, torch.bfloat16, [150, 64, 20, 1], 3, seed=21)
+    assert len(calls) == 1                                           # the prompts' step took it, the single tokens did not
+    monkeypatch.setattr(la, "PROMPT_KERNEL_MIN_TOKENS", 10 ** 9)
+    plain, _ = mixer_alone(entry, torch.bfloat16, [150, 64, 20, 1], 3, seed=21)
+    assert len(calls) == 1
+    for g, p, r in zip(got, plain, refs):
+        assert close(g, r, torch.bfloat16) and close(p, r, torch.bfloat16)
+        assert np.sqrt(np.mean((g - p) ** 2)) <= 0.02 * np.sqrt(np.mean(r ** 2))
+
+
 def test_a_far_token_reaches_through_a_slowly_decaying_state():
     """Decays close to 1: what the first tokens wrote is still read hundreds of tokens later, in the prompt and in the
     tokens decoded after it (a state that was lost or restarted would show)."""

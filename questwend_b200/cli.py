@@ -32,7 +32,7 @@ def parse_ids(text: str) -> list[int]:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="qw-cli", description="generate from token ids with a Qwen3 model on one B200")
+    ap = argparse.ArgumentParser(prog="qw-cli", description="generate from token ids with a model of a registered architecture on one B200")
     ap.add_argument("-m", dest="model", help="model folder (config.json + model.safetensors)")
     ap.add_argument("--random", metavar="CONFIG_JSON", help="instead of -m: a config.json; the weights are drawn from --seed")
     ap.add_argument("--save", metavar="DIR", help="with --random: write the model folder there (config.json + model.safetensors)")

@@ -81,7 +81,9 @@ def mixer_alone(entry, dtype, lens, extra, seed, width=48, slow_decay=False, sin
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("entry", [mh.mamba(), mh.mamba(heads=2, vdim=40, state=72, groups=1, norm_groups=1, conv=1),
-                                   mh.mamba(heads=4, vdim=8, state=20, groups=4, norm_groups=4, conv=8)])
+                                   mh.mamba(heads=4, vdim=8, state=20, groups=4, norm_groups=4, conv=8),
+                                   mh.mamba(heads=2, vdim=6, state=160, groups=2, norm_groups=3, conv=2),
+                                   mh.mamba(heads=1, vdim=3, state=264, groups=1, norm_groups=1, conv=2)])
 def test_mamba2_alone(entry, dtype):
     got, refs = mixer_alone(entry, dtype, [70, 3, 1], 6, seed=1)
     for g, r in zip(got, refs):
@@ -90,7 +92,9 @@ def test_mamba2_alone(entry, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("entry", [mh.delta(), mh.delta(heads=4, kv_heads=1, dim=72, vdim=8, conv=2),
-                                   mh.delta(heads=2, kv_heads=2, dim=8, vdim=40, conv=1)])
+                                   mh.delta(heads=2, kv_heads=2, dim=8, vdim=40, conv=1),
+                                   mh.delta(heads=2, kv_heads=1, dim=136, vdim=6, conv=3),
+                                   mh.delta(heads=1, kv_heads=1, dim=260, vdim=5, conv=2)])
 def test_gated_delta_rule_alone(entry, dtype):
     got, refs = mixer_alone(entry, dtype, [66, 2, 1], 6, seed=2)
     for g, r in zip(got, refs):

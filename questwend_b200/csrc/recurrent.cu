@@ -108,6 +108,23 @@ __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefe
 #define QWB_DELTA_CW_MAX 2      // ... and in the delta rule (a token's two sums over the rows sit in its chain: 2 measured best)
 #endif
 
+// Sums over the warp of 16 values a lane at once: at every step a lane hands half of its values to its partner and adds
+// the partner's other half, so the warp needs 8 + 4 + 2 + 1 + 1 shuffles instead of 16 x 5.  Afterwards lane l holds the
+// total of value (l >> 1) in v[0] (both lanes of a pair hold it).  The order of the additions is fixed.
+__device__ __forceinline__ void warp_sum16(float (&v)[16], int lane) {
+#pragma unroll
+    for (int half = 8, offset = 16; half >= 1; half >>= 1, offset >>= 1) {
+        const bool upper = lane & offset;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+            const float keep = upper ? v[i + half] : v[i];
+            const float send = upper ? v[i] : v[i + half];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, offset);
+        }
+    }
+    v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
+}
+
 // Mamba-2.  Per head h (group g = h / (H / G)), per token:
 //     dt = softplus(dt_raw + dt_bias[h]);  S = exp(-exp(A_log[h]) dt) S + dt B x^T;  y = S^T C + D[h] x
 //   xbc [T, ldx] float: x [H * P] | B [G * N] | C [G * N] (after convolution and SiLU)
@@ -188,15 +205,32 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const float* __restrict_
                 }
             }
         }
+        if (TB * CW == 16) {                                        // the round's 16 sums at once; lane 2 i writes sum i
+            float v16[16];
 #pragma unroll
-        for (int j = 0; j < TB; ++j)
+            for (int j = 0; j < TB; ++j)
 #pragma unroll
-            for (int c = 0; c < CW; ++c) acc[j][c] = warp_sum(acc[j][c]);
+                for (int c = 0; c < CW; ++c) v16[(j * CW + c) & 15] = acc[j][c];
+            warp_sum16(v16, lane);
+            const int mine = lane >> 1, j = mine / CW, c = mine - j * CW;
+            float x_mine = 0.f;
 #pragma unroll
-        for (int j = 0; j < TB; ++j)
+            for (int jj = 0; jj < TB; ++jj)
 #pragma unroll
-            for (int c = 0; c < CW; ++c)
-                if (lane == 0 && tc + j < t1) y[(size_t)(tc + j) * inner + h * P + p0 + c] = acc[j][c] + dskip * xv[j][c];
+                for (int cc = 0; cc < CW; ++cc)
+                    if (jj * CW + cc == mine) x_mine = xv[jj][cc];
+            if (!(lane & 1) && tc + j < t1) y[(size_t)(tc + j) * inner + h * P + p0 + c] = v16[0] + dskip * x_mine;
+        } else {
+#pragma unroll
+            for (int j = 0; j < TB; ++j)
+#pragma unroll
+                for (int c = 0; c < CW; ++c) acc[j][c] = warp_sum(acc[j][c]);
+#pragma unroll
+            for (int j = 0; j < TB; ++j)
+#pragma unroll
+                for (int c = 0; c < CW; ++c)
+                    if (lane == 0 && tc + j < t1) y[(size_t)(tc + j) * inner + h * P + p0 + c] = acc[j][c] + dskip * xv[j][c];
+        }
     }
     if (write_state) {
 #pragma unroll

@@ -133,15 +133,32 @@ __global__ void latent_attn_kernel(const float* __restrict__ q_abs, const float*
     const int p0 = pos0[b];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    for (int idx = threadIdx.x; idx < ROWS * dk; idx += blockDim.x) {
-        const int r = idx / dk, d = idx - r * dk;
-        const int qi = r / HB, hi = r - qi * HB;
-        float v = 0.f;
-        if (qi < nq && hi < nh) {
-            const int t = t0 + q0 + qi, h = h0 + hi;
-            v = d < L ? q_abs[((size_t)h * n_tok + t) * L + d] : q_rot[((size_t)t * H + h) * R + (d - L)];
+    if (L % 4 == 0 && R % 4 == 0 && (uintptr_t)q_abs % 16 == 0 && (uintptr_t)q_rot % 16 == 0) {      // four values a load
+        const int pieces = dk / 4;
+#pragma unroll 2
+        for (int idx = threadIdx.x; idx < ROWS * pieces; idx += blockDim.x) {
+            const int r = idx / pieces, d = (idx - r * pieces) * 4;
+            const int qi = r / HB, hi = r - qi * HB;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (qi < nq && hi < nh) {
+                const int t = t0 + q0 + qi, h = h0 + hi;
+                v = *reinterpret_cast<const float4*>(d < L ? q_abs + ((size_t)h * n_tok + t) * L + d
+                                                           : q_rot + ((size_t)t * H + h) * R + (d - L));
+            }
+            float* dst = Qs + r * dk + d;
+            dst[0] = v.x * scale; dst[1] = v.y * scale; dst[2] = v.z * scale; dst[3] = v.w * scale;
         }
-        Qs[idx] = v * scale;
+    } else {
+        for (int idx = threadIdx.x; idx < ROWS * dk; idx += blockDim.x) {
+            const int r = idx / dk, d = idx - r * dk;
+            const int qi = r / HB, hi = r - qi * HB;
+            float v = 0.f;
+            if (qi < nq && hi < nh) {
+                const int t = t0 + q0 + qi, h = h0 + hi;
+                v = d < L ? q_abs[((size_t)h * n_tok + t) * L + d] : q_rot[((size_t)t * H + h) * R + (d - L)];
+            }
+            Qs[idx] = v * scale;
+        }
     }
 
     float m[RPW], l[RPW], acc[RPW][NC];
@@ -162,11 +179,31 @@ __global__ void latent_attn_kernel(const float* __restrict__ q_abs, const float*
 
     for (int kt = (k_first / BK) * BK; kt <= k_last; kt += BK) {
         __syncthreads();
-        for (int idx = threadIdx.x; idx < BK * dk; idx += blockDim.x) {
-            const int j = idx / dk, d = idx - j * dk, key = kt + j;
-            float kv = 0.f;
-            if (key <= k_last) kv = to_f32(pool[((size_t)pages[key / page_size] * page_size + key % page_size) * dk + d]);
-            Ks[j * (dk + 1) + d] = kv;
+        constexpr int VEC = Vec16<T>::N;
+        if (dk % VEC == 0 && (uintptr_t)pool % 16 == 0) {           // a cached row is whole 16-byte pieces: one load a piece
+            const int pieces = dk / VEC;
+#pragma unroll 2
+            for (int idx = threadIdx.x; idx < BK * pieces; idx += blockDim.x) {
+                const int j = idx / pieces, d = (idx - j * pieces) * VEC, key = kt + j;
+                float vals[VEC];
+                if (key <= k_last) {
+                    const Vec16<T> piece = *reinterpret_cast<const Vec16<T>*>(
+                        pool + ((size_t)pages[key / page_size] * page_size + key % page_size) * dk + d);
+                    piece.get(vals);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) vals[e] = 0.f;
+                }
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) Ks[j * (dk + 1) + d + e] = vals[e];
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < BK * dk; idx += blockDim.x) {
+                const int j = idx / dk, d = idx - j * dk, key = kt + j;
+                float kv = 0.f;
+                if (key <= k_last) kv = to_f32(pool[((size_t)pages[key / page_size] * page_size + key % page_size) * dk + d]);
+                Ks[j * (dk + 1) + d] = kv;
+            }
         }
         __syncthreads();
         float s[RPW];
@@ -245,6 +282,9 @@ __global__ void latent_attn_kernel(const float* __restrict__ q_abs, const float*
     }
 }
 
+#define QWB_LATENT_MAX_L 512
+#define QWB_LATENT_MAX_ROW 1024
+
 // The runs of one (sequence, head) merged: out = sum_r acc_r e^(m_r - M) / (sum_r l_r e^(m_r - M) + e^(sink - M)),
 // M = max(m_r, sink), over the runs that hold a visible key, in their order.  grid (H, B).
 template <typename T>
@@ -263,10 +303,26 @@ __global__ void latent_combine_kernel(const float* __restrict__ part_acc, const 
     float denom = sink ? expf(sink[h] - M) : 0.f;
     for (int r = r0; r <= r1; ++r) denom += part_ml[2 * (base + r) + 1] * expf(part_ml[2 * (base + r)] - M);
     const float inv = 1.f / denom;
-    for (int d = threadIdx.x; d < L; d += blockDim.x) {
-        float v = 0.f;
-        for (int r = r0; r <= r1; ++r) v += part_acc[(base + r) * L + d] * expf(part_ml[2 * (base + r)] - M);
-        out[((size_t)h * n_tok + b) * L + d] = from_f32<T>(v * inv);
+    __shared__ float wts[128];                                      // the runs' factors e^(m_r - M), 128 runs at a time
+    float v[QWB_LATENT_MAX_L / 128];
+#pragma unroll
+    for (int i = 0; i < QWB_LATENT_MAX_L / 128; ++i) v[i] = 0.f;
+    for (int first = r0; first <= r1; first += 128) {
+        const int count = min(128, r1 - first + 1);
+        __syncthreads();
+        if ((int)threadIdx.x < count) wts[threadIdx.x] = expf(part_ml[2 * (base + first + threadIdx.x)] - M);
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < QWB_LATENT_MAX_L / 128; ++i) {
+            const int d = threadIdx.x + i * 128;
+            if (d < L)
+                for (int r = 0; r < count; ++r) v[i] += part_acc[(base + first + r) * L + d] * wts[r];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < QWB_LATENT_MAX_L / 128; ++i) {
+        const int d = threadIdx.x + i * 128;
+        if (d < L) out[((size_t)h * n_tok + b) * L + d] = from_f32<T>(v[i] * inv);
     }
 }
 
@@ -307,8 +363,6 @@ static int launch_latent_attn(const float* q_abs, const float* q_rot, const void
     return 0;
 }
 
-#define QWB_LATENT_MAX_L 512
-#define QWB_LATENT_MAX_ROW 1024
 
 // max_runs > 0: every sequence brings one token (n_tok = B) and no sequence holds more than max_runs * 64 keys after the
 // step; the keys are cut into runs of 64 (by the key's index, whatever else is in the batch), a block a run, and merged.

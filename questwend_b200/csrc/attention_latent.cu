@@ -107,9 +107,10 @@ extern "C" int qwb_latent_prep(const float* q, const float* dkv, const float* c_
 // Attention.  A block takes 16 rows, a row being a (token, head) pair: HB = min(H, 16) heads of TQ = 16 / HB
 // consecutive tokens of one sequence, so that the rows share the key tiles.  4 warps, 4 rows each; keys in tiles
 // of 32, one key per lane.  Prompts and single tokens are the same code (a single token is a tile of one token).
+// A single-token step of few sequences takes 4 rows a block instead (a row a warp): four times the blocks.
 //   q_abs [H, T, L] float, q_rot [T, H, R] float;  out [H, T, L] in the cache's dtype
 // ---------------------------------------------------------------------------------
-template <typename T, int NC>       // NC * 32 >= L
+template <typename T, int NC, int RPW>      // NC * 32 >= L; RPW rows a warp: 4, or 1 to spread a small step over more blocks
 __global__ void latent_attn_kernel(const float* __restrict__ q_abs, const float* __restrict__ q_rot, const T* __restrict__ pool,
                                    const int* __restrict__ page_table, const int* __restrict__ cu_seqlens,
                                    const int* __restrict__ pos0, const float* __restrict__ sink, T* __restrict__ out, int n_tok,
@@ -117,7 +118,7 @@ __global__ void latent_attn_kernel(const float* __restrict__ q_abs, const float*
                                    int run_keys, int max_runs, float* __restrict__ part_acc, float* __restrict__ part_ml) {
     pdl_wait();
     pdl_launch_dependents();
-    constexpr int ROWS = 16, BK = 32, RPW = 4;
+    constexpr int ROWS = 4 * RPW, BK = 32;
     const int dk = L + R;
     extern __shared__ float smem[];
     float* Qs = smem;                       // [ROWS][dk], scaled
@@ -334,25 +335,30 @@ static int launch_latent_attn(const float* q_abs, const float* q_rot, const void
                               int max_new, int H, int L, int R, int page_size, int table_width, float scale, int window,
                               int max_runs, float* part_acc, float* part_ml, cudaStream_t stream) {
     const int dk = L + R;
-    const size_t smem = ((size_t)16 * dk + 32 * (dk + 1)) * sizeof(float);
-    const int HB = H < 16 ? H : 16, TQ = 16 / HB;
     const int run_keys = max_runs > 0 ? QWB_LATENT_RUN_KEYS : 0;
+    // few blocks (a single-token step of few sequences): a row a warp, so that four times as many blocks share the work
+    const bool narrow = max_runs > 0 && (long long)B * max_runs * ((H + 15) / 16) < 120;
+    const int rows = narrow ? 4 : 16;
+    const size_t smem = ((size_t)rows * dk + 32 * (dk + 1)) * sizeof(float);
+    const int HB = H < rows ? H : rows, TQ = rows / HB;
     dim3 grid(max_runs > 0 ? max_runs : (max_new + TQ - 1) / TQ, (H + HB - 1) / HB, B);
     const int nc = (L + 31) / 32;
-#define QWB_LAUNCH_LATENT(NC)                                                                                          \
+#define QWB_LAUNCH_LATENT1(NC, RPW)                                                                                    \
     do {                                                                                                               \
         if (smem > 48 * 1024) {                                                                                        \
-            cudaError_t e = cudaFuncSetAttribute(latent_attn_kernel<T, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t e = cudaFuncSetAttribute(latent_attn_kernel<T, NC, RPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "latent_attn: %s", cudaGetErrorString(e));             \
         }                                                                                                              \
-        qwb_launch(latent_attn_kernel<T, NC>, grid, 128, smem, stream, q_abs, q_rot, (const T*)pool, page_table,       \
+        qwb_launch(latent_attn_kernel<T, NC, RPW>, grid, 128, smem, stream, q_abs, q_rot, (const T*)pool, page_table,  \
                    cu_seqlens, pos0, sink, (T*)out, n_tok, H, L, R, page_size, table_width, scale, window, run_keys,   \
                    max_runs, part_acc, part_ml);                                                                      \
     } while (0)
+#define QWB_LAUNCH_LATENT(NC) do { if (narrow) QWB_LAUNCH_LATENT1(NC, 1); else QWB_LAUNCH_LATENT1(NC, 4); } while (0)
     if (nc <= 2) QWB_LAUNCH_LATENT(2);
     else if (nc <= 4) QWB_LAUNCH_LATENT(4);
     else if (nc <= 8) QWB_LAUNCH_LATENT(8);
     else QWB_LAUNCH_LATENT(16);
+#undef QWB_LAUNCH_LATENT1
 #undef QWB_LAUNCH_LATENT
     if (int rc = qwb_check_launch("latent_attn")) return rc;
     if (max_runs > 0) {

@@ -56,7 +56,7 @@ def mixer_alone(entry, dtype, lens, extra, seed, width=48, slow_decay=False, sin
         v = torch.from_numpy(w[t.name])
         held[t.name] = v.to(dtype if t.role == "matrix" else torch.float32).to(DEV)
     part.bind(held)
-    cache = CacheManager([(part.kv_spec(), part.state_spec(), None)], 2048, 8, 1024, dtype, DEV)
+    cache = CacheManager([(part.kv_spec(), part.state_spec(), None)], max(2048, sum(lens) + 64 * len(lens) + 512), 8, 2048, dtype, DEV)
     unit = cache.unit_cache(0)
     rng = np.random.default_rng(seed + 1)
     xs = [pmv.round_bf16(rng.standard_normal((n + extra, width))) for n in lens]
@@ -164,6 +164,16 @@ def test_window_edges_show(window):
     a = pmv.latent_attention(x, w, "l0.mix.", entry["mixer"], 1e-5)
     b = pmv.latent_attention(x, w, "l0.mix.", wrong["mixer"], 1e-5)
     assert np.abs(a - b).max() > 1000 * FP32_TOL * np.abs(a).max()      # the plain implementation does tell them apart
+
+
+def test_single_tokens_of_many_long_sequences():
+    """Eight sequences of about a thousand keys: enough runs of keys that a block takes 16 (token, head) rows (few
+    sequences take 4), and the merge adds up 16 runs; with and without a window."""
+    for window in (0, 300):
+        entry = mh.latent(heads=2, dim=16, rot_dim=4, vdim=16, kv_rank=16, q_rank=16, window=window)
+        got, refs = mixer_alone(entry, torch.float32, [1000, 1010, 990, 1001, 1000, 1000, 999, 1003], 2, seed=9)
+        for g, r in zip(got, refs):
+            assert close(g[-2:], r[-2:], torch.float32)
 
 
 def test_the_sink_counts():

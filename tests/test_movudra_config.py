@@ -117,3 +117,15 @@ def test_the_plain_implementation_cut_anywhere_is_itself():
     tokens = np.random.default_rng(0).integers(0, 32, 20).tolist()
     whole = pmv.forward(mh.ONES, w, tokens)
     assert np.allclose(pmv.forward(mh.ONES, w, tokens[:7]), whole[:7], rtol=0, atol=1e-9)
+
+
+def test_the_benchmark_s_sizes_are_configurations():
+    """``bench.py --model movudra`` builds these two: both must parse, and the Movudra one within the kernels' limits."""
+    import bench
+    cfg, plan = plan_of(bench.movudra_sizes())
+    assert len(plan.layers) == 6 and [l["type"] for l in cfg.layers[:3]] == ["channel_delta", "latent_attention", "mamba2"]
+    assert sum(int(np.prod(t.shape)) for t in plan.manifest()) > 2e9
+    small = bench.movudra_sizes(width=1024, repeats=1, window=128, vocab=1000)
+    assert config_from_dict(small).layers[1]["mixer"]["mask"]["size"] == 128
+    beside = config_from_dict(bench.qwen3_beside())
+    assert (beside.hidden_size, beside.num_hidden_layers, beside.vocab_size) == (2048, 6, 32768)

@@ -449,24 +449,70 @@ __global__ void rmsnorm_onto_kernel(const float* __restrict__ y, const float* __
     }
 }
 
+// The same for rows of up to 4 x ITERS x 256 values that are whole 16-byte pieces: the row of y stays in registers and a
+// thread's loads are issued together (a step of one token is one block: its two passes are what it takes).
+template <typename TOut, int ITERS>
+__global__ void __launch_bounds__(256)
+rmsnorm_onto_rows_kernel(const float* __restrict__ y, const float* __restrict__ w, float* h, TOut* __restrict__ cast, int D, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float red[32];
+    const size_t at = (size_t)blockIdx.x * D;
+    const float4* y4 = reinterpret_cast<const float4*>(y + at);
+    float4* h4 = reinterpret_cast<float4*>(h + at);
+    float4 v[ITERS], g[ITERS], r[ITERS];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < ITERS; ++k) {
+        const int i = threadIdx.x + k * 256;
+        const bool in = i < D / 4;
+        v[k] = in ? y4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        g[k] = in ? reinterpret_cast<const float4*>(w)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        r[k] = in ? h4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    }
+    const float scale = rsqrtf(block_sum(ss, red) / (float)D + eps);
+#pragma unroll
+    for (int k = 0; k < ITERS; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < D / 4) {
+            const float4 o = make_float4(r[k].x + v[k].x * scale * g[k].x, r[k].y + v[k].y * scale * g[k].y,
+                                         r[k].z + v[k].z * scale * g[k].z, r[k].w + v[k].w * scale * g[k].w);
+            h4[i] = o;
+            if (cast) Pack4<TOut>::store(cast + at + 4 * (size_t)i, o.x, o.y, o.z, o.w);
+        }
+    }
+}
+
 extern "C" int qwb_rmsnorm_onto(const float* y, const float* w, float* h, void* cast, int cast_dtype, int T, int D, float eps,
                                 cudaStream_t stream) {
     if (T <= 0) return 0;
     if (D <= 0) return qwb_fail(QWB_ERR_ARG, "rmsnorm_onto: bad width %d", D);
+    if (cast && cast_dtype != QWB_DT_BF16 && cast_dtype != QWB_DT_F32) return qwb_fail(QWB_ERR_ARG, "rmsnorm_onto: unknown dtype %d", cast_dtype);
+    const bool to_bf16 = cast && cast_dtype == QWB_DT_BF16;
+    const bool vec = D % 4 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)h % 16 == 0 && (!cast || (uintptr_t)cast % 16 == 0);
+    if (vec && D / 4 <= 4 * 256) {
+        if (D / 4 <= 2 * 256) {
+            if (to_bf16) qwb_launch(rmsnorm_onto_rows_kernel<bf16, 2>, T, 256, 0, stream, y, w, h, (bf16*)cast, D, eps);
+            else qwb_launch(rmsnorm_onto_rows_kernel<float, 2>, T, 256, 0, stream, y, w, h, (float*)cast, D, eps);
+        } else {
+            if (to_bf16) qwb_launch(rmsnorm_onto_rows_kernel<bf16, 4>, T, 256, 0, stream, y, w, h, (bf16*)cast, D, eps);
+            else qwb_launch(rmsnorm_onto_rows_kernel<float, 4>, T, 256, 0, stream, y, w, h, (float*)cast, D, eps);
+        }
+        return qwb_check_launch("rmsnorm_onto");
+    }
     const size_t smem = (size_t)D * sizeof(float);
     if (smem > 200 * 1024) return qwb_fail(QWB_ERR_ARG, "rmsnorm_onto: width %d does not fit in shared memory", D);
     const int block = D >= 1024 ? 256 : 128;
     cudaError_t e = cudaSuccess;
-    if (cast && cast_dtype == QWB_DT_BF16) {
+    if (to_bf16) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_onto_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm_onto: %s", cudaGetErrorString(e));
         qwb_launch(rmsnorm_onto_kernel<bf16>, T, block, smem, stream, y, w, h, (bf16*)cast, D, eps);
-    } else if (!cast || cast_dtype == QWB_DT_F32) {
+    } else {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_onto_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm_onto: %s", cudaGetErrorString(e));
         qwb_launch(rmsnorm_onto_kernel<float>, T, block, smem, stream, y, w, h, (float*)cast, D, eps);
-    } else {
-        return qwb_fail(QWB_ERR_ARG, "rmsnorm_onto: unknown dtype %d", cast_dtype);
     }
     return qwb_check_launch("rmsnorm_onto");
 }

@@ -54,14 +54,41 @@ __global__ void conv_tail_kernel(const float* __restrict__ x, int ld, float* tai
     for (int r = 0; r < taps - 1; ++r) tl[(size_t)r * C + c] = keep[r];
 }
 
+// A step of one token per sequence: the convolution and the new tail by one thread per (sequence, channel).
+__global__ void short_conv_step_kernel(const float* __restrict__ x, int ld, const float* __restrict__ w, const float* __restrict__ bias,
+                                       float* tail, const int* __restrict__ slots, float* __restrict__ out, int B, int C, int taps,
+                                       int act, int update_tail) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int c = blockIdx.y * blockDim.x + threadIdx.x, b = blockIdx.x;
+    if (c >= C || b >= B) return;
+    float* tl = tail + (size_t)slots[b] * (taps - 1) * C;
+    const float cur = x[(size_t)b * ld + c];
+    float acc = (bias ? bias[c] : 0.f) + w[c * taps + taps - 1] * cur;
+    float keep[QWB_CONV_MAX_TAPS];
+    for (int r = 0; r < taps - 1; ++r) {
+        keep[r] = tl[(size_t)r * C + c];
+        acc += w[c * taps + r] * keep[r];
+    }
+    out[(size_t)b * C + c] = act ? silu_f(acc) : acc;
+    if (update_tail) {
+        for (int r = 0; r + 1 < taps - 1; ++r) tl[(size_t)r * C + c] = keep[r + 1];
+        if (taps > 1) tl[(size_t)(taps - 2) * C + c] = cur;
+    }
+}
+
 extern "C" int qwb_short_conv(const float* x, int ld, const float* w, const float* bias, float* tail, const int* tok_seq,
                               const int* cu_seqlens, const int* slots, float* out, int T, int B, int C, int taps, int act,
-                              int update_tail, cudaStream_t stream) {
+                              int update_tail, int single_token, cudaStream_t stream) {
     if (T <= 0 || B <= 0) return 0;
     if (C <= 0 || taps < 1 || taps > QWB_CONV_MAX_TAPS || ld < C)
         return qwb_fail(QWB_ERR_ARG, "short_conv: %d channels, %d taps (1 to %d), row stride %d", C, taps, QWB_CONV_MAX_TAPS, ld);
     if (B > 65535 || C > 65535 * 128) return qwb_fail(QWB_ERR_ARG, "short_conv: %d sequences or %d channels are too many", B, C);
     const int block = C >= 256 ? 256 : 128;
+    if (single_token && T == B) {
+        qwb_launch(short_conv_step_kernel, dim3(B, (C + block - 1) / block), block, 0, stream, x, ld, w, bias, tail, slots, out, B, C, taps, act, update_tail);
+        return qwb_check_launch("short_conv_step");
+    }
     qwb_launch(short_conv_kernel, dim3(T, (C + block - 1) / block), block, 0, stream, x, ld, w, bias, (const float*)tail, tok_seq, cu_seqlens, slots, out, T, C, taps, act);
     if (int rc = qwb_check_launch("short_conv")) return rc;
     if (update_tail && taps > 1) {

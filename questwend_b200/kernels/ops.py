@@ -692,8 +692,9 @@ def short_conv(x: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, 
     out = torch.empty((T, channels), dtype=torch.float32, device=x.device)
     _call("recurrent", "qwb_short_conv", ctypes.c_void_p(x.data_ptr() + 4 * col0), _i(ld), _ptr(weight), _ptr(bias),
           _ptr(tail), _ptr(ctx.tok_seq), _ptr(ctx.cu_seqlens), _ptr(ctx.slots), _ptr(out), _i(T), _i(ctx.n_seqs),
-          _i(channels), _i(taps), _i(1 if activation else 0), _i(1 if update_tail else 0), _stream(),
-          kernels=2 if (update_tail and taps > 1) else 1)
+          _i(channels), _i(taps), _i(1 if activation else 0), _i(1 if update_tail else 0),
+          _i(1 if ctx.single_token else 0), _stream(),
+          kernels=2 if (update_tail and taps > 1 and not ctx.single_token) else 1)
     return out
 
 

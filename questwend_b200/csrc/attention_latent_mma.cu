@@ -9,7 +9,8 @@
 // rounded to bfloat16 for the second product, as in every tensor-core attention.
 //
 // Block = 64 queries of one (sequence, head), 4 warps of 16 rows; keys in tiles of 64.  Q, K and V tiles sit in shared
-// memory with rows padded by 16 bytes (conflict-free ldmatrix).
+// memory with rows padded by 16 bytes (conflict-free ldmatrix); K and V have two buffers, and the next tile is copied
+// in (cp.async) while this one is multiplied.
 #include "common.cuh"
 
 #define LM_BQ 64
@@ -28,6 +29,14 @@ __device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uin
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// 16 bytes from global to shared memory without passing through registers; `bytes` 0 writes zeros (src must still be valid)
+__device__ __forceinline__ void cp_async16(bf16* dst, const bf16* src, int bytes) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -46,21 +55,19 @@ latent_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
     const int ldq = DQ + LM_PAD, ldv = DV + LM_PAD;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);           // [64][ldq]
-    bf16* Ks = Qs + LM_BQ * ldq;                            // [64][ldq]
-    bf16* Vs = Ks + LM_BK * ldq;                            // [64][ldv]
+    bf16* Kbuf = Qs + LM_BQ * ldq;                          // [2][64][ldq]
+    bf16* Vbuf = Kbuf + 2 * LM_BK * ldq;                    // [2][64][ldv]
 
     const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * LM_BQ;
     const int t0 = cu_seqlens[b], n = cu_seqlens[b + 1] - t0;
     if (q0 >= n) return;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
-    // the queries of the tile (rows beyond the sequence: zeros)
+    // the queries of the tile (rows beyond the sequence: zeros), in the first copy group
     for (int idx = tid; idx < LM_BQ * (DQ / 8); idx += blockDim.x) {
         const int r = idx / (DQ / 8), c = (idx - r * (DQ / 8)) * 8;
-        uint4 val = zero4;
-        if (q0 + r < n) val = *reinterpret_cast<const uint4*>(q + ((size_t)(t0 + q0 + r) * H + h) * DQ + c);
-        *reinterpret_cast<uint4*>(Qs + r * ldq + c) = val;
+        const bool in = q0 + r < n;
+        cp_async16(Qs + r * ldq + c, q + ((size_t)(t0 + (in ? q0 + r : 0)) * H + h) * DQ + c, in ? 16 : 0);
     }
 
     float o[NV][4];
@@ -73,24 +80,34 @@ latent_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
     const int k_hi = min(n, q0 + LM_BQ) - 1;
     const int k_lo = window > 0 ? max(0, q0 - window + 1) : 0;
     const int nv_used = DV / 8;
+    const int kt0 = (k_lo / LM_BK) * LM_BK;
 
-    for (int kt = (k_lo / LM_BK) * LM_BK; kt <= k_hi; kt += LM_BK) {
-        __syncthreads();                                            // the last tile is no longer read (and Q is written)
+    auto copy_tile = [&](int kt, int stage) {                       // one commit group a tile
+        bf16* Kd = Kbuf + stage * LM_BK * ldq;
+        bf16* Vd = Vbuf + stage * LM_BK * ldv;
         for (int idx = tid; idx < LM_BK * (DQ / 8); idx += blockDim.x) {
             const int r = idx / (DQ / 8), c = (idx - r * (DQ / 8)) * 8;
-            uint4 val = zero4;
-            if (kt + r < n) {
-                const size_t t = (size_t)(t0 + kt + r);
-                val = c < K ? *reinterpret_cast<const uint4*>(k_plain + (t * H + h) * K + c)
-                            : *reinterpret_cast<const uint4*>(kr + t * ld_kr + (c - K));
-            }
-            *reinterpret_cast<uint4*>(Ks + r * ldq + c) = val;
+            const bool in = kt + r < n;
+            const size_t t = (size_t)(t0 + (in ? kt + r : 0));
+            cp_async16(Kd + r * ldq + c, c < K ? k_plain + (t * H + h) * K + c : kr + t * ld_kr + (c - K), in ? 16 : 0);
         }
         for (int idx = tid; idx < LM_BK * (DV / 8); idx += blockDim.x) {
             const int r = idx / (DV / 8), c = (idx - r * (DV / 8)) * 8;
-            uint4 val = zero4;
-            if (kt + r < n) val = *reinterpret_cast<const uint4*>(v + ((size_t)(t0 + kt + r) * H + h) * DV + c);
-            *reinterpret_cast<uint4*>(Vs + r * ldv + c) = val;
+            const bool in = kt + r < n;
+            cp_async16(Vd + r * ldv + c, v + ((size_t)(t0 + (in ? kt + r : 0)) * H + h) * DV + c, in ? 16 : 0);
+        }
+        cp_async_commit();
+    };
+    copy_tile(kt0, 0);
+
+    for (int kt = kt0, it = 0; kt <= k_hi; kt += LM_BK, ++it) {
+        const bf16* Ks = Kbuf + (it & 1) * LM_BK * ldq;
+        const bf16* Vs = Vbuf + (it & 1) * LM_BK * ldv;
+        if (kt + LM_BK <= k_hi) {                                   // the next tile into the other buffer (its last readers
+            copy_tile(kt + LM_BK, (it + 1) & 1);                    // passed the barrier at the end of the round before)
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
         }
         __syncthreads();
 
@@ -158,6 +175,7 @@ latent_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
                 }
             }
         }
+        __syncthreads();                                            // this buffer may be copied into again
     }
 
     if (sink) {                                                     // one more term in the denominator, with no value
@@ -189,7 +207,7 @@ extern "C" int qwb_latent_prefill_mma(const void* q, const void* k_plain, const 
     if (B > 65535 || H > 65535) return qwb_fail(QWB_ERR_ARG, "latent_prefill_mma: batch %d or heads %d are too many", B, H);
     for (const void* p : {q, k_plain, kr, v, (const void*)out})
         if ((uintptr_t)p % 16) return qwb_fail(QWB_ERR_ARG, "latent_prefill_mma: a tensor is not 16-byte aligned");
-    const size_t smem = ((size_t)2 * LM_BQ * (K + R + LM_PAD) + (size_t)LM_BK * (DV + LM_PAD + 8)) * sizeof(bf16);
+    const size_t smem = ((size_t)3 * LM_BQ * (K + R + LM_PAD) + (size_t)2 * LM_BK * (DV + LM_PAD)) * sizeof(bf16);
     if (smem > 220 * 1024) return qwb_fail(QWB_ERR_ARG, "latent_prefill_mma: %d + %d query values do not fit in shared memory", K, R);
     const dim3 grid((max_new + LM_BQ - 1) / LM_BQ, H, B);
 #define QWB_LM(NV)                                                                                                              \

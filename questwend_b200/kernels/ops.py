@@ -821,8 +821,9 @@ def latent_prep(q: torch.Tensor, dkv: torch.Tensor, c_weight: torch.Tensor, cos,
 
 def latent_prefill_fits(dtype: torch.dtype, dim: int, rot_dim: int, vdim: int, rank: int) -> bool:
     """Whether the tensor-core prompt kernel takes these head sizes (else the plain kernel does)."""
+    tiles = (3 * 64 * (dim + rot_dim + 8) + 2 * 64 * (vdim + 8)) * 2       # bytes of shared memory: Q, two K, two V tiles
     return (dtype == torch.bfloat16 and dim % 8 == 0 and rot_dim % 8 == 0 and vdim % 8 == 0 and (dim + rot_dim) % 16 == 0
-            and vdim <= 256 and rank % 8 == 0 and dim + rot_dim <= 512)
+            and vdim <= 256 and rank % 8 == 0 and tiles <= 220 * 1024)
 
 
 def latent_prefill(q: torch.Tensor, k_plain: torch.Tensor, rows: torch.Tensor, v: torch.Tensor, ctx, sink, scale: float,

@@ -112,7 +112,8 @@ def test_latent_attention_alone(entry, dtype):
 
 @pytest.mark.parametrize("window", [0, 1, 2, 63, 64, 65, 100])
 @pytest.mark.parametrize("sizes", [dict(heads=3, dim=24, rot_dim=8, vdim=40, kv_rank=40), dict(heads=2, dim=64, rot_dim=16, vdim=64, kv_rank=48),
-                                   dict(heads=1, dim=8, rot_dim=8, vdim=8, kv_rank=8, q_rank=8)])
+                                   dict(heads=1, dim=8, rot_dim=8, vdim=8, kv_rank=8, q_rank=8),
+                                   dict(heads=2, dim=24, rot_dim=8, vdim=136, kv_rank=16, q_rank=16)])
 def test_whole_prompts_on_the_tensor_cores(sizes, window, monkeypatch):
     """bfloat16 prompts that start their sequences take the tensor-core kernel (keys and values per head made from the
     latents): against the plain implementation, and against the kernel that scores the latents themselves, for windows
@@ -216,6 +217,14 @@ def test_router_weights_are_the_scores_themselves():
     assert np.allclose(weight.cpu().numpy(), [[s[0, 0], s[0, 4]], [0.2, 0.2]], atol=1e-6)    # not renormalised
     _, renorm = ops.moe_route(z, 2, renormalize=True)
     assert np.allclose(renorm.cpu().numpy().sum(-1), 1.0, atol=1e-6)
+
+
+def test_the_prompt_kernel_is_refused_where_its_tiles_do_not_fit():
+    from questwend_b200.kernels import ops
+    assert ops.latent_prefill_fits(torch.bfloat16, 128, 64, 128, 512)
+    assert not ops.latent_prefill_fits(torch.bfloat16, 448, 64, 256, 512)        # 3 x 64 x 520 + 2 x 64 x 264 values: too much
+    assert not ops.latent_prefill_fits(torch.float32, 128, 64, 128, 512)
+    assert not ops.latent_prefill_fits(torch.bfloat16, 100, 28, 128, 512)        # parts in multiples of 8
 
 
 def test_paired_rotation_table():

@@ -305,6 +305,34 @@ def test_whole_prompts_decoding_batches_and_reuse(models, name, dtype):
     assert eng.cache.slots.n_free == eng.max_batch and all(f == eng.cache.n_pages for f in eng.cache.free_pages())
 
 
+@pytest.mark.parametrize("layers", [[(mh.mamba(heads=2, vdim=8, state=16, groups=2, norm_groups=2), mh.dense(ff=24)), (mh.delta(heads=2, kv_heads=2, dim=8, vdim=8), None)],
+                                    [(mh.latent(heads=2, dim=8, rot_dim=8, vdim=8, kv_rank=16, q_rank=8, window=3), mh.moe(ff=8, experts=4, top=2))]],
+                         ids=["no_cache_rows", "no_state"])
+def test_models_with_one_kind_of_mixer_only(layers, tmp_path):
+    """A model without attention has no cache pages at all, one without recurrent layers no per-slot state: the cache
+    manager, the step function and generation (CUDA graphs too) take both."""
+    import questwend_b200 as qw
+    cfgd = mh.config(layers, width=24, vocab=40)
+    w = mh.draw_weights(cfgd, 31)
+    folder = mh.write_folder(str(tmp_path / "m"), cfgd, w)
+    eng = Engine.from_folder(folder, dtype="float32", max_tokens=512, max_batch=3)
+    tokens = np.random.default_rng(2).integers(0, 40, 70).tolist()
+    ref = pmv.forward(cfgd, w, tokens)
+    (s,) = eng.open_sequences(1)
+    rows = list(all_rows(eng, s, tokens[:66]))
+    for t in tokens[66:]:
+        rows.append(eng.step([StepEntry(s, [t], [0])]).double().cpu().numpy()[0])
+    eng.close_sequences([s])
+    assert close(np.stack(rows), ref, torch.float32)
+    for use_graph in (True, False):
+        out = qw.generate(eng, [tokens[:5], tokens[:1]], max_new_tokens=8, use_graph=use_graph)
+        for p, r in zip([tokens[:5], tokens[:1]], out):
+            full = pmv.forward(cfgd, w, p + r.tokens)
+            for j, tok in enumerate(r.tokens):
+                row = full[len(p) - 1 + j]
+                assert row.max() - row[tok] <= 2 * FP32_TOL * np.abs(full).max()
+
+
 def test_generation_through_the_library_loop(models):
     """Greedy generation with the engine's own loop, scheduler, device sampler and CUDA graphs: two batches in slots that
     are used again, one request ending early; every chosen token is the plain implementation's choice."""

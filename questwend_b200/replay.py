@@ -23,21 +23,33 @@ import os
 import sys
 
 
+PAGE = 64
+MIN_SLOTS, MAX_SLOTS = 64, 256
+
+
+def cache_sizes(max_tokens: int) -> dict:
+    """How the engine is sized for a trace whose live requests hold up to ``max_tokens`` tokens, padding not counted.
+    Every live request holds whole pages of 64 tokens, so it may leave most of its last page unused: the pools get a
+    page more for every request that can be alive, and there are slots for as many requests as there are pages
+    (at least 64, at most 256: a slot also holds the fixed-size state of every recurrent layer)."""
+    pages = max(1, -(-max_tokens // PAGE))
+    slots = min(MAX_SLOTS, max(MIN_SLOTS, pages))
+    return {"max_tokens": max_tokens + PAGE * slots, "max_batch": slots}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
     ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+                    help="most tokens live requests hold at any time (the cache adds room for their unused page ends)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
     from .engine.engine import Engine, StepEntry     # after parsing: --help needs no GPU
     os.makedirs(args.out, exist_ok=True)
-    # every live request holds at least one page of 64 tokens, so there are never more of them than pages
-    engine = Engine.from_folder(args.model, dtype=args.dtype, device=args.device, max_tokens=args.max_tokens,
-                                max_batch=max(1, -(-args.max_tokens // 64)))
+    engine = Engine.from_folder(args.model, dtype=args.dtype, device=args.device, **cache_sizes(args.max_tokens))
     slot_of: dict = {}
     for line in sys.stdin:
         line = line.strip()

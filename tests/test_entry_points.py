@@ -129,7 +129,7 @@ def test_replay_protocol_with_a_stand_in_engine(tmp_path, monkeypatch, capsys):
     monkeypatch.setattr(sys, "stdin", io.StringIO("".join(json.dumps(s) + "\n" for s in steps) + "\n"))
     out = tmp_path / "out"
     assert replay.main(["--model", "somewhere", "--dtype", "float32", "--out", str(out), "--max-tokens", "200"]) == 0
-    assert made["folder"] == "somewhere" and made["dtype"] == "float32" and made["max_tokens"] == 200 and made["max_batch"] == 4
+    assert made["folder"] == "somewhere" and made["dtype"] == "float32" and made["max_tokens"] == 200 + 64 * 64 and made["max_batch"] == 64     # a page more for each of 64 slots
     assert capsys.readouterr().out.split() == ["done", "0", "done", "1", "done", "2", "done", "3"]
     assert sorted(os.listdir(out)) == ["0.f32", "2.f32", "3.f32"]                  # step 1 wanted nothing
     assert np.fromfile(out / "0.f32", dtype="<f4").reshape(3, 3).tolist() == [[0, 5, 0], [0, 3, 2], [1, 9, 0]]

@@ -14,6 +14,10 @@ state for layers that have it (:115-116, 493-494), zeroed at start (:614-630).  
   page pool of its own and a page table of its own (one page id is valid in every
   unit of its group).  ``max_tokens`` sizes each pool: the most tokens that live
   sequences may hold together, each sequence's count rounded up to whole pages.
+* A mixer may ask for several kinds of rows (its ``kv_spec`` is then a tuple): each lands in a group of its own.  A
+  spec with ``stride`` s > 1 holds one row for every s tokens (a row per complete block of s tokens), so a sequence of
+  n tokens holds n // s rows there and its group's pool is that much smaller; a spec with ``value_dim`` has values of
+  another size than its keys.
 * The pools are zeroed once, when they are made.  Nothing is zeroed when a page or
   slot is handed out again: kernels never use what lies beyond a sequence's length
   (the tensor-core kernels multiply it by probability 0, so it must be finite: it is
@@ -81,6 +85,11 @@ def pages_for(n_tokens: int) -> int:
     return (n_tokens + PAGE_SIZE - 1) // PAGE_SIZE
 
 
+def group_pages_for(spec: KVSpec, n_tokens: int) -> int:
+    """Pages that a sequence of ``n_tokens`` tokens holds in a group of this spec (one row per ``stride`` tokens)."""
+    return pages_for(n_tokens // max(1, spec.stride))
+
+
 @dataclass
 class _KVGroup:
     spec: KVSpec
@@ -116,7 +125,7 @@ class CacheManager:
         self.slots = FreeList(max_slots, "slot")
         self.lengths = [0] * max_slots
         self._groups: list[_KVGroup] = []
-        self._unit_group: dict[int, tuple[int, int]] = {}     # schedule index -> (group id, index in group)
+        self._unit_group: dict[int, list] = {}                # schedule index -> [(group id, index in group)], one per spec
         self._unit_state: dict[int, _StateUnit] = {}
         self._cache_of: dict[int, int] = {}
 
@@ -126,21 +135,25 @@ class CacheManager:
                 self._cache_of[i] = cache_of
                 continue
             if kv is not None:
-                by_spec.setdefault(kv, []).append(i)
+                for spec in ((kv,) if isinstance(kv, KVSpec) else tuple(kv)):
+                    by_spec.setdefault(spec, []).append(i)
             if state is not None:
                 single = isinstance(state, StateSpec)
                 specs = (state,) if single else tuple(state)
                 storages = tuple(torch.zeros((max_slots, *sp.shape), dtype=sp.dtype, device=self.device) for sp in specs)
                 self._unit_state[i] = _StateUnit(specs, storages, single)
         for gid, (spec, members) in enumerate(by_spec.items()):
-            shape = (len(members), self.n_pages, spec.n_kv_heads, PAGE_SIZE, spec.head_dim)
+            # a strided group holds a row per complete block: a share of the tokens' pages, and the last page of every
+            # live sequence may be partly used
+            n_pages = self.n_pages if spec.stride <= 1 else min(self.n_pages, pages_for(-(-max_tokens // spec.stride)) + max_slots)
+            shape = (len(members), n_pages, spec.n_kv_heads, PAGE_SIZE, spec.head_dim)
             # zeroed once (the reference zeroes its cache too, core/runtime.cpp:614-630): a page's unused tail is
             # multiplied by probability 0 in the tensor-core kernels and must hold finite numbers
             k = torch.zeros(shape, dtype=dtype, device=self.device)
-            v = torch.zeros(shape, dtype=dtype, device=self.device) if spec.values else None
-            self._groups.append(_KVGroup(spec, members, FreeList(self.n_pages, "page"), k, v, {}))
+            v = torch.zeros((*shape[:-1], spec.v_dim), dtype=dtype, device=self.device) if spec.values else None
+            self._groups.append(_KVGroup(spec, members, FreeList(n_pages, "page"), k, v, {}))
             for j, u in enumerate(members):
-                self._unit_group[u] = (gid, j)
+                self._unit_group.setdefault(u, []).append((gid, j))
 
     # ------------------------------------------------------------------ what layers see
     def n_groups(self) -> int:
@@ -152,15 +165,18 @@ class CacheManager:
     def unit_cache(self, unit: int) -> UnitCache:
         owner = self._cache_of.get(unit, unit)
         writable = owner == unit
-        gid = k = v = state = None
-        if owner in self._unit_group:
-            gid, j = self._unit_group[owner]
-            k = self._groups[gid].k[j]
-            v = self._groups[gid].v[j] if self._groups[gid].v is not None else None
+        state = None
+        views = []
+        for gid, j in self._unit_group.get(owner, []):
+            g = self._groups[gid]
+            views.append(UnitCache(gid, g.k[j], g.v[j] if g.v is not None else None, None, writable))
         if owner in self._unit_state:
             st = self._unit_state[owner]
             state = st.storages[0] if st.single else st.storages
-        return UnitCache(gid, k, v, state, writable)
+        if not views:
+            return UnitCache(None, None, None, state, writable)
+        first = views[0]
+        return UnitCache(first.group_id, first.k_pool, first.v_pool, state, writable, more=tuple(views[1:]))
 
     def bytes_held(self) -> int:
         n = 0
@@ -219,19 +235,28 @@ class CacheManager:
                 raise CacheFull(f"slot {slot} would hold {n_tokens} tokens; the longest sequence allowed "
                                 f"is {self.max_seq_len}")
             for gi, g in enumerate(self._groups):
-                need[gi] += max(0, pages_for(n_tokens) - len(g.pages[slot]))
+                need[gi] += max(0, group_pages_for(g.spec, n_tokens) - len(g.pages[slot]))
         for gi, g in enumerate(self._groups):
             if need[gi] > g.pool.n_free:
                 raise CacheFull(f"{need[gi]} more pages wanted, {g.pool.n_free} of {g.pool.n} free "
                                 f"(max_tokens={self.max_tokens})")
         for slot, n_tokens in wants.items():
             for g in self._groups:
-                more = pages_for(n_tokens) - len(g.pages[slot])
+                more = group_pages_for(g.spec, n_tokens) - len(g.pages[slot])
                 if more > 0:
                     g.pages[slot].extend(g.pool.take(more))
 
     def advance(self, slot: int, n_new: int) -> None:
         self.lengths[slot] += n_new
+
+    def room(self, slot: int) -> int:
+        """How many more tokens the slot can take before any of its groups needs another page."""
+        n = self.length(slot)
+        room = self.max_seq_len - n
+        for g in self._groups:
+            stride = max(1, g.spec.stride)
+            room = min(room, len(g.pages[slot]) * PAGE_SIZE * stride + stride - 1 - n)
+        return room
 
     def truncate(self, slot: int, length: int) -> None:
         """Forget the tokens from ``length`` on (the reference's rewind for attention-only models,
@@ -242,7 +267,7 @@ class CacheManager:
             raise CacheError(f"slot {slot} holds {self.lengths[slot]} tokens, cannot truncate to {length}")
         self.lengths[slot] = length
         for g in self._groups:
-            keep = pages_for(length)
+            keep = group_pages_for(g.spec, length)
             g.pool.give_back(g.pages[slot][keep:])
             del g.pages[slot][keep:]
 

@@ -520,31 +520,61 @@ extern "C" int qwb_rmsnorm_onto(const float* y, const float* w, float* h, void* 
 // ---------------------------------------------------------------------------------
 // out[t, f] = act(x[t, f] + bias[f]) for F columns of a float matrix with rows of ld values (the caller offsets the
 // pointer to the first column); out [T, F] float or bfloat16 (may be x itself when float and ld = F).
-// act 0: none; 1: relu squared; 2: gelu (tanh form); 3: silu.  bias may be null.
+// act 0: none; 1: relu squared; 2: gelu (tanh form); 3: silu; 4: xIELU with two learned numbers p, q (`params`):
+// v > 0: softplus(p) v^2 + v / 2;  v <= 0: (1/2 + softplus(q)) (e^v - 1 - v) + v / 2.  bias may be null.
 // ---------------------------------------------------------------------------------
+__device__ __forceinline__ float softplus32(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
 template <typename TOut>
-__global__ void bias_act_kernel(const float* x, int ld, const float* __restrict__ bias, TOut* out, size_t n, int F, int act) {
+__global__ void bias_act_kernel(const float* x, int ld, const float* __restrict__ bias, TOut* out, size_t n, int F, int act,
+                                const float* __restrict__ params) {
     pdl_wait();
     pdl_launch_dependents();
+    float up = 0.f, down = 0.f;
+    if (act == 4) { up = softplus32(params[0]); down = 0.5f + softplus32(params[1]); }
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / F, f = i - t * F;
         float v = x[t * ld + f] + (bias ? bias[f] : 0.f);
         if (act == 1) { v = fmaxf(v, 0.f); v *= v; }
         else if (act == 2) v = 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
         else if (act == 3) v = v / (1.f + expf(-v));
+        else if (act == 4) v = v > 0.f ? up * v * v + 0.5f * v : down * (expm1f(v) - v) + 0.5f * v;
         out[i] = from_f32<TOut>(v);
     }
 }
 
-extern "C" int qwb_bias_act(const float* x, int ld, const float* bias, void* out, int out_dtype, int T, int F, int act, cudaStream_t stream) {
+extern "C" int qwb_bias_act(const float* x, int ld, const float* bias, void* out, int out_dtype, int T, int F, int act,
+                            const float* params, cudaStream_t stream) {
     if (T <= 0 || F <= 0) return 0;
     if (ld < F) return qwb_fail(QWB_ERR_ARG, "bias_act: rows of %d values hold no %d columns", ld, F);
-    if (act < 0 || act > 3) return qwb_fail(QWB_ERR_ARG, "bias_act: unknown activation %d", act);
+    if (act < 0 || act > 4) return qwb_fail(QWB_ERR_ARG, "bias_act: unknown activation %d", act);
+    if (act == 4 && !params) return qwb_fail(QWB_ERR_ARG, "bias_act: this activation needs its two numbers");
     const size_t n = (size_t)T * F;
     const int block = 256;
     const int grid = (int)((n + block - 1) / block < 148 * 16 ? (n + block - 1) / block : 148 * 16);
-    if (out_dtype == QWB_DT_F32) qwb_launch(bias_act_kernel<float>, grid, block, 0, stream, x, ld, bias, (float*)out, n, F, act);
-    else if (out_dtype == QWB_DT_BF16) qwb_launch(bias_act_kernel<bf16>, grid, block, 0, stream, x, ld, bias, (bf16*)out, n, F, act);
+    if (out_dtype == QWB_DT_F32) qwb_launch(bias_act_kernel<float>, grid, block, 0, stream, x, ld, bias, (float*)out, n, F, act, params);
+    else if (out_dtype == QWB_DT_BF16) qwb_launch(bias_act_kernel<bf16>, grid, block, 0, stream, x, ld, bias, (bf16*)out, n, F, act, params);
     else return qwb_fail(QWB_ERR_ARG, "bias_act: unknown dtype %d", out_dtype);
     return qwb_check_launch("bias_act");
+}
+
+// ---------------------------------------------------------------------------------
+// Logits in place: v <- v * scale, then cap * tanh(v / cap) if cap > 0.
+// ---------------------------------------------------------------------------------
+__global__ void scale_softcap_kernel(float* x, size_t n, float scale, float cap) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const float inv = cap > 0.f ? 1.f / cap : 0.f;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = x[i] * scale;
+        x[i] = cap > 0.f ? cap * tanhf(v * inv) : v;
+    }
+}
+
+extern "C" int qwb_scale_softcap(float* x, long long n, float scale, float cap, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int block = 256;
+    const long long grid = (n + block - 1) / block;
+    qwb_launch(scale_softcap_kernel, (unsigned)(grid > 148 * 16 ? 148 * 16 : grid), block, 0, stream, x, (size_t)n, scale, cap);
+    return qwb_check_launch("scale_softcap");
 }

@@ -17,9 +17,11 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); 
 // out[t, c] = act( bias[c] + sum_j w[c, j] * in(i - (taps - 1 - j), c) ),  i = the token's index in this step,
 // in(i < 0) = the tail: tail[slot, taps - 1 + i, c] (the last taps - 1 inputs of the sequence before this step,
 // zero for a new sequence).  x [T, ld] is read at column c (the caller offsets the pointer), out is [T, C].
+// in_bias, if given, is added to every input x before it is convolved (a projection's bias: the tail holds inputs with
+// it, the zeros before a sequence's start stay zeros).
 // ---------------------------------------------------------------------------------
 __global__ void short_conv_kernel(const float* __restrict__ x, int ld, const float* __restrict__ w, const float* __restrict__ bias,
-                                  const float* tail, const int* __restrict__ tok_seq, const int* __restrict__ cu_seqlens,
+                                  const float* __restrict__ in_bias, const float* tail, const int* __restrict__ tok_seq, const int* __restrict__ cu_seqlens,
                                   const int* __restrict__ slots, float* __restrict__ out, int T, int C, int taps, int act) {
     pdl_wait();
     pdl_launch_dependents();
@@ -28,18 +30,19 @@ __global__ void short_conv_kernel(const float* __restrict__ x, int ld, const flo
     const int b = tok_seq[t];
     const int i = t - cu_seqlens[b];
     float acc = bias ? bias[c] : 0.f;
+    const float ib = in_bias ? in_bias[c] : 0.f;
     const float* tl = tail + (size_t)slots[b] * (taps - 1) * C;
     for (int j = 0; j < taps; ++j) {
         const int src = i - (taps - 1 - j);
-        const float v = src >= 0 ? x[(size_t)(t - (taps - 1 - j)) * ld + c] : tl[(size_t)(taps - 1 + src) * C + c];
+        const float v = src >= 0 ? x[(size_t)(t - (taps - 1 - j)) * ld + c] + ib : tl[(size_t)(taps - 1 + src) * C + c];
         acc += w[c * taps + j] * v;
     }
     out[(size_t)t * C + c] = act ? silu_f(acc) : acc;
 }
 
 // The tail after the step: the last taps - 1 inputs of each sequence (new ones, then what is left of the old tail).
-__global__ void conv_tail_kernel(const float* __restrict__ x, int ld, float* tail, const int* __restrict__ cu_seqlens,
-                                 const int* __restrict__ slots, int B, int C, int taps) {
+__global__ void conv_tail_kernel(const float* __restrict__ x, int ld, const float* __restrict__ in_bias, float* tail,
+                                 const int* __restrict__ cu_seqlens, const int* __restrict__ slots, int B, int C, int taps) {
     pdl_wait();
     pdl_launch_dependents();
     const int c = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
@@ -47,23 +50,24 @@ __global__ void conv_tail_kernel(const float* __restrict__ x, int ld, float* tai
     const int t0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - t0;
     float* tl = tail + (size_t)slots[b] * (taps - 1) * C;
     float keep[QWB_CONV_MAX_TAPS];
+    const float ib = in_bias ? in_bias[c] : 0.f;
     for (int r = 0; r < taps - 1; ++r) {
         const int idx = n_new - (taps - 1) + r;
-        keep[r] = idx >= 0 ? x[(size_t)(t0 + idx) * ld + c] : tl[(size_t)(r + n_new) * C + c];
+        keep[r] = idx >= 0 ? x[(size_t)(t0 + idx) * ld + c] + ib : tl[(size_t)(r + n_new) * C + c];
     }
     for (int r = 0; r < taps - 1; ++r) tl[(size_t)r * C + c] = keep[r];
 }
 
 // A step of one token per sequence: the convolution and the new tail by one thread per (sequence, channel).
 __global__ void short_conv_step_kernel(const float* __restrict__ x, int ld, const float* __restrict__ w, const float* __restrict__ bias,
-                                       float* tail, const int* __restrict__ slots, float* __restrict__ out, int B, int C, int taps,
+                                       const float* __restrict__ in_bias, float* tail, const int* __restrict__ slots, float* __restrict__ out, int B, int C, int taps,
                                        int act, int update_tail) {
     pdl_wait();
     pdl_launch_dependents();
     const int c = blockIdx.y * blockDim.x + threadIdx.x, b = blockIdx.x;
     if (c >= C || b >= B) return;
     float* tl = tail + (size_t)slots[b] * (taps - 1) * C;
-    const float cur = x[(size_t)b * ld + c];
+    const float cur = x[(size_t)b * ld + c] + (in_bias ? in_bias[c] : 0.f);
     float acc = (bias ? bias[c] : 0.f) + w[c * taps + taps - 1] * cur;
     float keep[QWB_CONV_MAX_TAPS];
     for (int r = 0; r < taps - 1; ++r) {
@@ -77,7 +81,7 @@ __global__ void short_conv_step_kernel(const float* __restrict__ x, int ld, cons
     }
 }
 
-extern "C" int qwb_short_conv(const float* x, int ld, const float* w, const float* bias, float* tail, const int* tok_seq,
+extern "C" int qwb_short_conv(const float* x, int ld, const float* w, const float* bias, const float* in_bias, float* tail, const int* tok_seq,
                               const int* cu_seqlens, const int* slots, float* out, int T, int B, int C, int taps, int act,
                               int update_tail, int single_token, cudaStream_t stream) {
     if (T <= 0 || B <= 0) return 0;
@@ -86,13 +90,13 @@ extern "C" int qwb_short_conv(const float* x, int ld, const float* w, const floa
     if (B > 65535 || C > 65535 * 128) return qwb_fail(QWB_ERR_ARG, "short_conv: %d sequences or %d channels are too many", B, C);
     const int block = C >= 256 ? 256 : 128;
     if (single_token && T == B) {
-        qwb_launch(short_conv_step_kernel, dim3(B, (C + block - 1) / block), block, 0, stream, x, ld, w, bias, tail, slots, out, B, C, taps, act, update_tail);
+        qwb_launch(short_conv_step_kernel, dim3(B, (C + block - 1) / block), block, 0, stream, x, ld, w, bias, in_bias, tail, slots, out, B, C, taps, act, update_tail);
         return qwb_check_launch("short_conv_step");
     }
-    qwb_launch(short_conv_kernel, dim3(T, (C + block - 1) / block), block, 0, stream, x, ld, w, bias, (const float*)tail, tok_seq, cu_seqlens, slots, out, T, C, taps, act);
+    qwb_launch(short_conv_kernel, dim3(T, (C + block - 1) / block), block, 0, stream, x, ld, w, bias, in_bias, (const float*)tail, tok_seq, cu_seqlens, slots, out, T, C, taps, act);
     if (int rc = qwb_check_launch("short_conv")) return rc;
     if (update_tail && taps > 1) {
-        qwb_launch(conv_tail_kernel, dim3((C + block - 1) / block, B), block, 0, stream, x, ld, tail, cu_seqlens, slots, B, C, taps);
+        qwb_launch(conv_tail_kernel, dim3((C + block - 1) / block, B), block, 0, stream, x, ld, in_bias, tail, cu_seqlens, slots, B, C, taps);
         return qwb_check_launch("conv_tail");
     }
     return 0;

@@ -200,7 +200,7 @@ class DecodeRunner:
                     self.tables[g].copy_(self.tables_host[g], non_blocking=True)
                     self._copied = torch.cuda.Event()
                     self._copied.record()
-                room = min(room, min(c * ops.PAGE_SIZE - n for c, n in zip(counts, lengths)))
+            room = min(room, min(cache.room(s) for s in self.slots))
             self._bucket = length_bucket(max(lengths) + 1)
             self._room = min(room, self._bucket - max(lengths))
             self._graph = {}

@@ -25,15 +25,20 @@ class Model:
         self.blocks = []
         for layer in plan.layers:
             position = None
-            if layer.position is not None:
-                key = (layer.position.kind, tuple(sorted(layer.position.params.items())))
-                if key not in self._positions:          # layers with the same encoding share one object
-                    self._positions[key] = build_part("position", layer.position, runtime)
-                position = self._positions[key]
+            if isinstance(layer.position, (tuple, list)):       # a mixer that turns several things (keys, values)
+                position = tuple(None if spec is None else self._position(spec) for spec in layer.position)
+            elif layer.position is not None:
+                position = self._position(layer.position)
             self.blocks.append(build_part("block", layer.block, runtime, layer=layer, position=position))
         self.final_norm = build_part("norm", plan.final_norm, runtime)
         self.head = build_part("head", plan.head, runtime)
         self.schedule = list(plan.schedule)
+
+    def _position(self, spec):
+        key = (spec.kind, tuple(sorted(spec.params.items())))
+        if key not in self._positions:                  # layers with the same encoding share one object
+            self._positions[key] = build_part("position", spec, self.runtime)
+        return self._positions[key]
 
     # ---- weights
     def parts(self):
@@ -77,13 +82,23 @@ class Model:
         return out
 
     # ---- one step
-    def forward(self, ctx: StepContext, unit_caches: list[UnitCache], want_rows: torch.Tensor) -> torch.Tensor:
+    def forward(self, ctx: StepContext, unit_caches: list[UnitCache], want_rows: torch.Tensor, tap=None) -> torch.Tensor:
+        """``tap(run index, stream)``, if given, is called after every scheduled run with the residual stream as it
+        stands there (what is still to be added is added first: slower, for looking at a model layer by layer)."""
         for position in self._positions.values():       # the step's tables first: no layer's kernels find them half made
             position.prepare(ctx)
         h = self.embedding.forward(ctx.token_ids)
         delta = None
         for i, run in enumerate(self.schedule):
             h, delta = self.blocks[run.layer].forward(h, delta, ctx, unit_caches[i])
+            if tap is not None:
+                if delta is not None:
+                    if hasattr(delta, "add_onto"):
+                        delta.add_onto(h)
+                    else:
+                        h.add_(delta)
+                    delta = None
+                tap(i, h)
         if want_rows.numel() == 0:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=h.device)
         x = self.final_norm.forward(h, settle(h, delta, self.final_norm), rows=want_rows)

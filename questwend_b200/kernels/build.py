@@ -25,7 +25,8 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", 
               "--shared", "-Xcompiler", "-fPIC"]
 EXTRA_FLAGS: dict[str, list[str]] = {}
 NVCC_FLAGS += os.environ.get("QWB200_NVCC_FLAGS", "").split()      # more flags (-D switches) for experiments; part of the stamp
-MODULES = ("elementwise", "rope_kv", "attention", "attention_mma", "attention_tc", "attention_latent", "attention_latent_mma", "recurrent", "moe",
+MODULES = ("elementwise", "layernorm", "rope_kv", "attention", "attention_mma", "attention_tc", "attention_latent", "attention_latent_mma",
+           "attention_pool", "recurrent", "rglru", "moe",
            "gemm_small", "gemm_stream", "gemm_ring", "gemm_tc", "sampling")
 
 _lock = threading.Lock()

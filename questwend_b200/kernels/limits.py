@@ -45,3 +45,15 @@ def moe_refusal(experts: int, top: int) -> str | None:
     if experts <= 0 or not 1 <= top <= min(experts, MOE_MAX_TOP):
         return f"the router chooses 1 to {MOE_MAX_TOP} of its experts, not {top} of {experts}"
     return None
+
+
+POOL_ATTN_DIM_STEP = 8      # the window-and-blocks attention takes key and value sizes that are multiples of this ...
+POOL_ATTN_MAX_DIM = 256     # ... up to this (csrc/attention_pool.cu: QWB_POOL_MAX_DIM)
+
+
+def pool_attention_refusal(dim: int, vdim: int) -> str | None:
+    for what, n in (("key", dim), ("value", vdim)):
+        if n <= 0 or n % POOL_ATTN_DIM_STEP or n > POOL_ATTN_MAX_DIM:
+            return (f"the window-and-blocks attention takes {what} sizes that are multiples of {POOL_ATTN_DIM_STEP} up to "
+                    f"{POOL_ATTN_MAX_DIM}, not {n}")
+    return None

@@ -182,11 +182,12 @@ def rmsnorm_onto(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: fl
     return h if cast is None else cast
 
 
-ACTIVATIONS = {"none": 0, "relu2": 1, "gelu_tanh": 2, "silu": 3}
+ACTIVATIONS = {"none": 0, "relu2": 1, "gelu_tanh": 2, "silu": 3, "xielu": 4}
+ACTIVATION_PARAMS = {"xielu": 2}    # activations with learned numbers of their own, and how many
 
 
 def bias_act(x: torch.Tensor, bias: torch.Tensor | None, activation: str, out_dtype: torch.dtype,
-             col0: int = 0, n_cols: int | None = None) -> torch.Tensor:
+             col0: int = 0, n_cols: int | None = None, params: torch.Tensor | None = None) -> torch.Tensor:
     """act(x + bias) for float32 x [T, F], or for its columns ``col0 .. col0 + n_cols``; ``activation`` one of
     ``ACTIVATIONS``.  Returns [T, F] (or [T, n_cols]) in ``out_dtype``; a float32 result of whole rows replaces x.
     With no bias and no activation this is the cast of a (slice of a) 32-bit result to a product's operand dtype."""
@@ -201,13 +202,64 @@ def bias_act(x: torch.Tensor, bias: torch.Tensor | None, activation: str, out_dt
             raise KernelError(f"bias_act: bias of {bias.numel()} for rows of {F}")
     if activation not in ACTIVATIONS:
         raise KernelError(f"bias_act: unknown activation '{activation}'")
+    if activation in ACTIVATION_PARAMS:
+        if params is None:
+            raise KernelError(f"bias_act: activation '{activation}' needs its {ACTIVATION_PARAMS[activation]} numbers")
+        _need(params, "params", torch.float32, 1)
+        if params.numel() != ACTIVATION_PARAMS[activation]:
+            raise KernelError(f"bias_act: activation '{activation}' takes {ACTIVATION_PARAMS[activation]} numbers, got {params.numel()}")
+    else:
+        params = None
     whole = F == ld
     if whole and out_dtype == torch.float32 and bias is None and activation == "none":
         return x
     out = x if (out_dtype == torch.float32 and whole) else torch.empty((T, F), dtype=out_dtype, device=x.device)
     _call("elementwise", "qwb_bias_act", ctypes.c_void_p(x.data_ptr() + 4 * col0), _i(ld), _ptr(bias), _ptr(out),
-          _i(_dt(out_dtype)), _i(T), _i(F), _i(ACTIVATIONS[activation]), _stream())
+          _i(_dt(out_dtype)), _i(T), _i(F), _i(ACTIVATIONS[activation]), _ptr(params), _stream())
     return out
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor | None, eps: float, out_dtype: torch.dtype | None = None,
+              add: torch.Tensor | None = None, add_weight: torch.Tensor | None = None, add_eps: float | None = None,
+              write_sum: bool = False, rows: torch.Tensor | None = None) -> torch.Tensor | None:
+    """Layer norm with a weight and no bias over the rows of float32 ``x`` [T, D], 32-bit throughout:
+    (v - mean) / sqrt(mean of squared deviations + eps) * weight.
+
+    With ``add`` (float32 [T, D]) the rows normed are x + LN(add) * add_weight: the norm of a sublayer's output is added
+    first, and with ``write_sum`` that sum replaces x.  ``weight`` None: only that sum is made (returns None).  With
+    ``rows`` (int32) only those rows are normed and the output has one row per entry."""
+    _need(x, "x", torch.float32, 2)
+    T, D = x.shape
+    for name, t in (("weight", weight), ("add_weight", add_weight)):
+        if t is not None:
+            _need(t, name, torch.float32, 1)
+            if t.numel() != D:
+                raise KernelError(f"layernorm: {name} has {t.numel()} entries for rows of {D}")
+    if (add is None) != (add_weight is None):
+        raise KernelError("layernorm: a sublayer output and its norm's weight come together")
+    if add is not None:
+        _need(add, "add", torch.float32, 2)
+        if add.shape != x.shape:
+            raise KernelError(f"layernorm: add {tuple(add.shape)} does not match x {tuple(x.shape)}")
+    n_rows = T
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+        n_rows = rows.numel()
+    out = None
+    if weight is not None:
+        out = torch.empty((n_rows, D), dtype=out_dtype, device=x.device)
+    _call("layernorm", "qwb_layernorm", _ptr(x), _ptr(add), _ptr(add_weight), _f(eps if add_eps is None else add_eps),
+          _i(1 if write_sum else 0), _ptr(weight), _ptr(out), _i(_dt(out_dtype) if out is not None else DT_F32), _ptr(rows),
+          _i(n_rows), _i(D), _f(eps), _stream())
+    return out
+
+
+def scale_softcap(x: torch.Tensor, scale: float = 1.0, cap: float = 0.0) -> torch.Tensor:
+    """In place on float32 ``x``: x * scale, then cap * tanh(x / cap) if ``cap`` > 0 (logits)."""
+    _need(x, "x", torch.float32)
+    if scale != 1.0 or cap > 0:
+        _call("elementwise", "qwb_scale_softcap", _ptr(x), ctypes.c_longlong(x.numel()), _f(scale), _f(cap), _stream())
+    return x
 
 
 # ----------------------------------------------------------------------------- rope + cache write
@@ -673,11 +725,14 @@ CONV_MAX_TAPS = 8
 
 
 def short_conv(x: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: torch.Tensor | None,
-               tail: torch.Tensor, ctx, activation: bool = True, update_tail: bool = True) -> torch.Tensor:
+               tail: torch.Tensor, ctx, activation: bool = True, update_tail: bool = True,
+               in_bias: torch.Tensor | None = None) -> torch.Tensor:
     """Causal convolution over time, per channel, of columns ``col0 .. col0 + channels`` of float32 ``x`` [T, ld], with
     SiLU after it (``activation``).  ``weight`` [channels, taps]: the last tap is the current token's.  ``tail``
     [slots, taps - 1, channels] float32 holds each sequence's last inputs (zero for a new one) and is brought up to
-    date (``update_tail``).  ``ctx``: the step (tok_seq, cu_seqlens, slots).  Returns float32 [T, channels]."""
+    date (``update_tail``).  ``in_bias`` [channels] is added to every input before the convolution (the bias of the
+    projection that made x; the tail holds inputs with it).  ``ctx``: the step (tok_seq, cu_seqlens, slots).
+    Returns float32 [T, channels]."""
     _need(x, "x", torch.float32, 2)
     _need(weight, "weight", torch.float32, 2)
     _need(tail, "tail", torch.float32, 3)
@@ -687,11 +742,14 @@ def short_conv(x: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, 
         raise KernelError(f"short_conv: weight {tuple(weight.shape)} for columns {col0}..{col0 + channels} of {ld}")
     if tuple(tail.shape[1:]) != (taps - 1, channels):
         raise KernelError(f"short_conv: tail {tuple(tail.shape)} does not fit {taps} taps of {channels} channels")
-    if bias is not None:
-        _need(bias, "bias", torch.float32, 1)
+    for name, t in (("bias", bias), ("in_bias", in_bias)):
+        if t is not None:
+            _need(t, name, torch.float32, 1)
+            if t.numel() != channels:
+                raise KernelError(f"short_conv: {name} of {t.numel()} for {channels} channels")
     out = torch.empty((T, channels), dtype=torch.float32, device=x.device)
     _call("recurrent", "qwb_short_conv", ctypes.c_void_p(x.data_ptr() + 4 * col0), _i(ld), _ptr(weight), _ptr(bias),
-          _ptr(tail), _ptr(ctx.tok_seq), _ptr(ctx.cu_seqlens), _ptr(ctx.slots), _ptr(out), _i(T), _i(ctx.n_seqs),
+          _ptr(in_bias), _ptr(tail), _ptr(ctx.tok_seq), _ptr(ctx.cu_seqlens), _ptr(ctx.slots), _ptr(out), _i(T), _i(ctx.n_seqs),
           _i(channels), _i(taps), _i(1 if activation else 0), _i(1 if update_tail else 0),
           _i(1 if ctx.single_token else 0), _stream(),
           kernels=2 if (update_tail and taps > 1 and not ctx.single_token) else 1)
@@ -771,6 +829,139 @@ def gated_part_norm(y: torch.Tensor, gate: torch.Tensor, gate_col0: int, weight:
     _call("recurrent", "qwb_gated_part_norm", _ptr(y), ctypes.c_void_p(gate.data_ptr() + 4 * gate_col0), _i(gate.shape[1]),
           _ptr(weight), _i(weight.numel()), _ptr(out), _i(_dt(out_dtype)), _i(T), _i(n_parts), _i(D // n_parts), _f(eps),
           _i(0 if gate_first else 1), _stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- real-gated linear recurrent unit
+RGLRU_CHUNK = 64            # tokens per chunk of the three-pass scan ...
+RGLRU_CHUNKED_FROM = 256    # ... which steps whose longest sequence brings at least this many tokens take
+
+
+def block_gates(u: torch.Tensor, w_a: torch.Tensor, b_a: torch.Tensor, w_i: torch.Tensor, b_i: torch.Tensor):
+    """Two gates from block-diagonal matrices: float32 ``u`` [T, C] is cut into ``blocks`` equal parts, part b goes through
+    ``w_a[b]`` / ``w_i[b]`` ([blocks, n, n], stored [out, in], float32 or bfloat16; multiplied in float) plus the biases
+    [blocks, n] (float32), then sigmoid.  Returns (r, i), float32 [T, C]."""
+    _need(u, "u", torch.float32, 2)
+    T, C = u.shape
+    blocks = w_a.shape[0]
+    n = C // blocks if blocks else 0
+    for name, w, b in (("w_a", w_a, b_a), ("w_i", w_i, b_i)):
+        _need(w, name, w_a.dtype, 3)
+        _need(b, name + " bias", torch.float32)
+        if blocks * n != C or tuple(w.shape) != (blocks, n, n) or b.numel() != C:
+            raise KernelError(f"block_gates: {name} {tuple(w.shape)} with bias of {b.numel()} for {C} channels")
+    r = torch.empty((T, C), dtype=torch.float32, device=u.device)
+    i = torch.empty_like(r)
+    _call("rglru", "qwb_block_gates", _ptr(u), _ptr(w_a), _ptr(b_a), _ptr(w_i), _ptr(b_i), _ptr(r), _ptr(i), _i(_dt(w_a.dtype)),
+          _i(T), _i(C), _i(blocks), _stream())
+    return r, i
+
+
+def rglru_scan(u: torch.Tensor, r: torch.Tensor, i: torch.Tensor, lam: torch.Tensor, y: torch.Tensor, y_col0: int,
+               y_bias: torch.Tensor | None, state: torch.Tensor, ctx, sharpness: float, out_dtype: torch.dtype,
+               write_state: bool = True) -> torch.Tensor:
+    """The real-gated linear recurrence over a step's tokens, per channel: a = exp(-sharpness * r * softplus(lam)),
+    S = a S + sqrt(1 - a^2) * i * u, read out as S * gelu_tanh(y + y_bias).  ``u``, ``r``, ``i`` float32 [T, C]; the
+    second branch is columns ``y_col0 .. y_col0 + C`` of float32 ``y`` [T, ld]; ``state`` float32 [slots, C] is read and
+    written back.  Returns [T, C] in ``out_dtype``.  Long prompts go in chunks (three passes), everything else in order."""
+    for name, t in (("u", u), ("r", r), ("i", i)):
+        _need(t, name, torch.float32, 2)
+    _need(y, "y", torch.float32, 2)
+    _need(lam, "lam", torch.float32, 1)
+    _need(state, "state", torch.float32, 2)
+    T, C = u.shape
+    if r.shape != u.shape or i.shape != u.shape or lam.numel() != C or state.shape[1] != C or y.shape[0] != T or y_col0 + C > y.shape[1]:
+        raise KernelError(f"rglru_scan: u {tuple(u.shape)}, r {tuple(r.shape)}, i {tuple(i.shape)}, lam of {lam.numel()}, state "
+                          f"{tuple(state.shape)}, y {tuple(y.shape)} from column {y_col0}")
+    if y_bias is not None:
+        _need(y_bias, "y_bias", torch.float32, 1)
+    out = torch.empty((T, C), dtype=out_dtype, device=u.device)
+    chunk = max_chunks = 0
+    tables = scratch = None
+    if ctx.max_new >= RGLRU_CHUNKED_FROM:
+        chunk = RGLRU_CHUNK
+        max_chunks = -(-T // chunk) + ctx.n_seqs
+        tables = torch.empty((2 * max_chunks + ctx.n_seqs + 1,), dtype=torch.int32, device=u.device)
+        scratch = torch.empty((2 * max_chunks * C,), dtype=torch.float32, device=u.device)
+    _call("rglru", "qwb_rglru_scan", _ptr(u), _ptr(r), _ptr(i), _ptr(lam), ctypes.c_void_p(y.data_ptr() + 4 * y_col0),
+          _i(y.shape[1]), _ptr(y_bias), _ptr(state), _ptr(ctx.cu_seqlens), _ptr(ctx.slots), _ptr(out), _i(_dt(out_dtype)),
+          _i(ctx.n_seqs), _i(C), _f(sharpness), _i(1 if write_state else 0), _i(chunk), _i(max_chunks), _ptr(tables),
+          _ptr(scratch), _stream(), kernels=4 if chunk else 1)
+    return out
+
+
+# ----------------------------------------------------------------------------- window + pooled blocks attention
+POOL_MAX_DIM = 256          # csrc/attention_pool.cu: QWB_POOL_MAX_DIM
+
+
+def pool_prep(qkv: torch.Tensor, q_weight, k_weight, cos_qk, sin_qk, cos_v, sin_v, ctx, page_table, k_pool, v_pool,
+              n_heads: int, n_kv_heads: int, dim: int, vdim: int, rotary_dim: int, interleaved: bool, eps: float,
+              store_kv: bool = True) -> torch.Tensor:
+    """Per-head RMS norm of q and k (weights [dim] shared by the heads, or None), rotation of their first ``rotary_dim``
+    values, rotation of every value by its own position (``cos_v`` given), cache write.  ``qkv`` float32
+    [T, (H + G) * dim + G * vdim]; the pools [pages, G, 64, dim] / [pages, G, 64, vdim].  Returns q [T, H, dim] in the
+    cache's dtype."""
+    _need(qkv, "qkv", torch.float32, 2)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (n_heads + n_kv_heads) * dim + n_kv_heads * vdim:
+        raise KernelError(f"pool_prep: qkv {tuple(qkv.shape)} for {n_heads}+{n_kv_heads} heads of {dim}, values of {vdim}")
+    if tuple(k_pool.shape[1:]) != (n_kv_heads, PAGE_SIZE, dim) or tuple(v_pool.shape[1:]) != (n_kv_heads, PAGE_SIZE, vdim):
+        raise KernelError(f"pool_prep: pools {tuple(k_pool.shape)}, {tuple(v_pool.shape)} do not fit")
+    for name, t, n in (("q_weight", q_weight, dim), ("k_weight", k_weight, dim)):
+        if t is not None:
+            _need(t, name, torch.float32, 1)
+            if t.numel() != n:
+                raise KernelError(f"pool_prep: {name} of {t.numel()} for heads of {n}")
+    for name, t, n in (("cos_qk", cos_qk, rotary_dim), ("sin_qk", sin_qk, rotary_dim), ("cos_v", cos_v, vdim), ("sin_v", sin_v, vdim)):
+        if t is not None:
+            _need(t, name, torch.float32, 2)
+            if tuple(t.shape) != (T, n // 2):
+                raise KernelError(f"pool_prep: table {name} {tuple(t.shape)} for {T} tokens and {n} turned values")
+    q = torch.empty((T, n_heads, dim), dtype=k_pool.dtype, device=qkv.device)
+    _call("attention_pool", "qwb_pool_prep", _ptr(qkv), _ptr(q_weight), _ptr(k_weight), _ptr(cos_qk), _ptr(sin_qk), _ptr(cos_v),
+          _ptr(sin_v), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(page_table), _i(page_table.shape[1]), _ptr(q), _ptr(k_pool),
+          _ptr(v_pool), _i(_dt(k_pool.dtype)), _i(T), _i(n_heads), _i(n_kv_heads), _i(dim), _i(vdim),
+          _i(rotary_dim if cos_qk is not None else 0), _i(1 if interleaved else 0), _i(1 if cos_v is not None else 0), _f(eps),
+          _i(1 if store_kv else 0), _stream())
+    return q
+
+
+def pool_update(k_pool, v_pool, pk_pool, pv_pool, page_table, block_table, ctx, pool: int) -> None:
+    """The block rows (means of ``pool`` consecutive cached keys and values) of the blocks that this step completes."""
+    G, dim, vdim = k_pool.shape[1], k_pool.shape[3], v_pool.shape[3]
+    max_blocks = ctx.max_new // pool + 1
+    _call("attention_pool", "qwb_pool_update", _ptr(k_pool), _ptr(v_pool), _ptr(pk_pool), _ptr(pv_pool), _ptr(page_table),
+          _ptr(block_table), _i(page_table.shape[1]), _ptr(ctx.pos0), _ptr(ctx.seq_len), _i(_dt(k_pool.dtype)), _i(ctx.n_seqs),
+          _i(max_blocks), _i(G), _i(dim), _i(vdim), _i(pool), _stream())
+
+
+def pool_attention(q: torch.Tensor, k_pool, v_pool, pk_pool, pv_pool, page_table, block_table, ctx, cos_v, sin_v,
+                   scale: float, window: int, pool: int, interleaved: bool) -> torch.Tensor:
+    """Attention of a step's tokens over their window and the block rows before it.  ``q`` [T, H, dim] in the cache's
+    dtype; returns [T, H * vdim] in that dtype, each head turned back by the query's position if ``cos_v`` is given."""
+    _need(q, "q", k_pool.dtype, 3)
+    T, H, dim = q.shape
+    G, vdim = k_pool.shape[1], v_pool.shape[3]
+    out = torch.empty((T, H * vdim), dtype=q.dtype, device=q.device)
+    width = page_table.shape[1]
+    if block_table is not None and block_table.shape[1] != width:
+        raise KernelError("pool_attention: the two page tables differ in width")
+    if ctx.single_token:
+        lib = _lookup("attention_pool", "qwb_pool_decode_runs")[0]
+        block_runs = ctypes.c_int(0)
+        n_runs = lib.qwb_pool_decode_runs(_i(ctx.max_len), _i(window), _i(pool), ctypes.byref(block_runs))
+        lib.qwb_pool_decode_scratch_floats.restype = ctypes.c_longlong
+        scratch = torch.empty((lib.qwb_pool_decode_scratch_floats(_i(T), _i(H), _i(vdim), _i(n_runs)),), dtype=torch.float32,
+                              device=q.device)
+        _call("attention_pool", "qwb_pool_decode", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(pk_pool), _ptr(pv_pool),
+              _ptr(page_table), _ptr(block_table), _ptr(ctx.seq_len), _ptr(cos_v), _ptr(sin_v), _ptr(scratch), _ptr(out),
+              _i(_dt(q.dtype)), _i(T), _i(H), _i(G), _i(dim), _i(vdim), _i(width), _f(scale), _i(window), _i(pool),
+              _i(block_runs.value), _i(n_runs), _i(1 if interleaved else 0), _stream(), kernels=2)
+        return out
+    _call("attention_pool", "qwb_pool_prefill", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(pk_pool), _ptr(pv_pool), _ptr(page_table),
+          _ptr(block_table), _ptr(ctx.cu_seqlens), _ptr(ctx.pos0), _ptr(cos_v), _ptr(sin_v), _ptr(out), _i(_dt(q.dtype)),
+          _i(ctx.n_seqs), _i(ctx.max_new), _i(H), _i(G), _i(dim), _i(vdim), _i(width), _f(scale), _i(window), _i(pool),
+          _i(1 if interleaved else 0), _stream())
     return out
 
 

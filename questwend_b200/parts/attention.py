@@ -9,7 +9,7 @@ import math
 import torch
 
 from ..kernels import ops
-from ..kernels.limits import head_dim_refusal
+from ..kernels.limits import head_dim_refusal, pool_attention_refusal
 from ..weights.manifest import MATRIX, NORM_WEIGHT, VECTOR, TensorSpec
 from .base import KVSpec, Mixer, take_weight
 from .linear import kernel_modules as linear_modules, linear, linear_onto
@@ -117,4 +117,104 @@ class GroupedQueryAttention(Mixer):
         return linear(att, self.w_o)
 
 
+class WindowPoolAttention(Mixer):
+    """Grouped-query attention over a sliding window plus pooled blocks of what lies before it.  The query at position p
+    sees the keys j with p - ``window`` < j <= p and, beside them, one key and value for each block of ``pool`` positions
+    that lies wholly before the window (block b = positions b*pool .. b*pool + pool - 1, seen when b*pool + pool - 1 <=
+    p - window): the means of the block's cached keys and values.  Tokens and blocks share one softmax.  Keys and values
+    may differ in size.  Per-head RMS norm of q and k (``qk_norm``; one weight for all heads), a rotation of the first
+    part of q and k, and (``rotate_values``) a rotation of every whole value by its own position before it is cached,
+    undone on each head's output by the query's position.
+
+    params: hidden_size, n_heads, n_kv_heads, head_dim, value_dim, qk_norm (bool), norm_eps, window (0: all keys, no
+    blocks), pool (0: no blocks), scale (default 1/sqrt(head_dim)), rotate_values (bool), layout ("halves": pairs
+    (i, i + n/2); "interleaved": (2i, 2i + 1)), names (optional overrides).  ``position``: the encoding of q and k, or a
+    pair (q/k encoding, values' encoding); an encoding gives cos and sin [T, n/2].
+    The cache: keys and values per token, and (with blocks) a second pair of pools with a row per complete block."""
+
+    NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "q_norm": "q.norm", "k_norm": "k.norm"}
+    LAYOUTS = ("halves", "interleaved")
+
+    def __init__(self, spec, runtime, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.n_heads, self.n_kv_heads = int(p["n_heads"]), int(p["n_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.value_dim = int(p.get("value_dim", self.head_dim))
+        self.qk_norm = bool(p.get("qk_norm", False))
+        self.eps = float(p.get("norm_eps", 0.0))
+        self.window = int(p.get("window", 0) or 0)
+        self.pool = int(p.get("pool", 0) or 0) if self.window else 0
+        self.scale = float(p.get("scale", 1.0 / math.sqrt(self.head_dim)))
+        self.rotate_values = bool(p.get("rotate_values", False))
+        self.layout = str(p.get("layout", "halves"))
+        self.names = {**self.NAMES, **dict(p.get("names", {}))}
+        positions = position if isinstance(position, (tuple, list)) else (position, None)
+        self.position, self.value_position = positions[0], (positions[1] if len(positions) > 1 else None)
+        self.rotary_dim = getattr(self.position, "rotary_dim", 0) if self.position is not None else 0
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError(f"{self.n_heads} heads are not a multiple of {self.n_kv_heads} key/value heads")
+        if self.layout not in self.LAYOUTS:
+            raise ValueError(f"attention '{self.prefix}': layout '{self.layout}' is not one of {', '.join(self.LAYOUTS)}")
+        refusal = pool_attention_refusal(self.head_dim, self.value_dim)
+        if refusal:
+            raise ValueError(f"attention '{self.prefix}': {refusal}")
+        if self.rotary_dim > self.head_dim:
+            raise ValueError(f"rotary size {self.rotary_dim} exceeds the head size {self.head_dim}")
+        if self.rotate_values and (self.value_position is None or getattr(self.value_position, "rotary_dim", 0) != self.value_dim):
+            raise ValueError(f"attention '{self.prefix}': turned values need an encoding over all {self.value_dim} of a value")
+
+    def tensors(self):
+        q, kv, vv, D = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim, self.n_kv_heads * self.value_dim, self.hidden
+        n, px = self.names, self.prefix
+        out = [TensorSpec(px + n["q"], (q, D), MATRIX), TensorSpec(px + n["k"], (kv, D), MATRIX),
+               TensorSpec(px + n["v"], (vv, D), MATRIX), TensorSpec(px + n["o"], (D, self.n_heads * self.value_dim), MATRIX)]
+        if self.qk_norm:
+            out += [TensorSpec(px + n["q_norm"], (self.head_dim,), VECTOR, NORM_WEIGHT),
+                    TensorSpec(px + n["k_norm"], (self.head_dim,), VECTOR, NORM_WEIGHT)]
+        return out
+
+    def bind(self, weights):
+        n, px = self.names, self.prefix
+        self.w_qkv = torch.cat([take_weight(weights, px + n[x]) for x in "qkv"], dim=0).contiguous()
+        self.w_o = weights[px + n["o"]]
+        self.q_norm_w = self.k_norm_w = None
+        if self.qk_norm:
+            self.q_norm_w = weights[px + n["q_norm"]].to(torch.float32).contiguous()
+            self.k_norm_w = weights[px + n["k_norm"]].to(torch.float32).contiguous()
+
+    def kernel_modules(self):
+        return ("attention_pool", "rope_kv", *linear_modules(self.runtime.dtype))
+
+    def kv_spec(self):
+        tokens = KVSpec(self.n_kv_heads, self.head_dim, self.window, value_dim=self.value_dim)
+        if not self.pool:
+            return tokens
+        return (tokens, KVSpec(self.n_kv_heads, self.head_dim, self.window, value_dim=self.value_dim, stride=self.pool))
+
+    def forward(self, x, ctx, cache):
+        qkv = linear(x, self.w_qkv)
+        cos = sin = cos_v = sin_v = None
+        if self.position is not None and self.rotary_dim:
+            cos, sin = self.position.prepare(ctx)
+        if self.rotate_values:
+            cos_v, sin_v = self.value_position.prepare(ctx)
+        interleaved = self.layout == "interleaved"
+        table = ctx.page_tables[cache.group_id]
+        q = ops.pool_prep(qkv, self.q_norm_w, self.k_norm_w, cos, sin, cos_v, sin_v, ctx, table, cache.k_pool, cache.v_pool,
+                          self.n_heads, self.n_kv_heads, self.head_dim, self.value_dim, self.rotary_dim, interleaved, self.eps,
+                          store_kv=cache.writable)
+        pk = pv = block_table = None
+        if self.pool:
+            blocks = cache.more[0]
+            pk, pv, block_table = blocks.k_pool, blocks.v_pool, ctx.page_tables[blocks.group_id]
+            if cache.writable:
+                ops.pool_update(cache.k_pool, cache.v_pool, pk, pv, table, block_table, ctx, self.pool)
+        att = ops.pool_attention(q, cache.k_pool, cache.v_pool, pk, pv, table, block_table, ctx, cos_v, sin_v, self.scale,
+                                 self.window, self.pool, interleaved)
+        return linear(att, self.w_o)
+
+
 register_mixer("gqa", GroupedQueryAttention)
+register_mixer("window_pool_attention", WindowPoolAttention)

@@ -41,6 +41,13 @@ class KVSpec:
     window: int = 0
     values: bool = True         # False: one row per token and no separate values (a latent that is key and value at once);
                                 # the unit's ``v_pool`` is then None
+    value_dim: int = 0          # size of a value row where it differs from a key row's (0: the same)
+    stride: int = 1             # one cached row for every ``stride`` tokens of the sequence (a row per complete block of
+                                # tokens: pooled keys and values); a sequence of n tokens holds n // stride rows
+
+    @property
+    def v_dim(self) -> int:
+        return self.value_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -85,10 +92,12 @@ class UnitCache:
     """What one scheduled layer run sees of the cache: its own keys/values and
     state, or (``writable`` False) those of the run whose cache it reads."""
 
-    def __init__(self, group_id=None, k_pool=None, v_pool=None, state=None, writable=True):
+    def __init__(self, group_id=None, k_pool=None, v_pool=None, state=None, writable=True, more=()):
         self.group_id = group_id
         self.k_pool = k_pool        # [n_pages, Hkv, page_size, hd] or None
-        self.v_pool = v_pool
+        self.v_pool = v_pool        # [n_pages, Hkv, page_size, value size] or None
+        self.more = more            # for a mixer whose ``kv_spec`` is a tuple: a UnitCache (group_id, k_pool, v_pool) for
+                                    # each spec after the first
         self.state = state          # [n_slots, *shape], a tuple of such (one per StateSpec), or None
         self.writable = writable
 
@@ -140,10 +149,25 @@ class Part:
         return ()
 
 
+class NormedSum:
+    """A sublayer's output that is still to be normed and added onto the stream: h += norm(y).  A block with a norm on
+    its sublayers' outputs hands this on as ``delta``; a norm that says ``adds_normed_sums`` does both norms in one pass
+    over the row, anyone else calls ``add_onto``."""
+    __slots__ = ("y", "norm")
+
+    def __init__(self, y: torch.Tensor, norm: "Norm"):
+        self.y, self.norm = y, norm
+
+    def add_onto(self, h: torch.Tensor) -> torch.Tensor:
+        self.norm.add_normed(h, self.y)
+        return h
+
+
 class Norm(Part):
     """y = norm(x + delta) over rows; x float32 [T, D]."""
 
     adds_split_sums = False     # True: ``delta`` may also be a SplitSum (a product left as sums over pieces of k)
+    adds_normed_sums = False    # True: ``delta`` may also be a NormedSum whose norm is of this class
 
     def forward(self, x, delta=None, write_sum=False, rows=None, out_dtype=None) -> torch.Tensor:
         raise NotImplementedError
@@ -165,7 +189,9 @@ class Mixer(Part):
     """Mixes information between the positions of a sequence (attention here).
     x [T, D] in the engine's dtype -> float32 [T, D], to be added to the residual stream."""
 
-    def kv_spec(self) -> KVSpec | None:
+    def kv_spec(self) -> KVSpec | tuple | None:
+        """What the mixer keeps per token: one ``KVSpec``, or a tuple of them (the first is found in the unit's
+        ``k_pool`` / ``v_pool`` / ``group_id``, the others in ``UnitCache.more``)."""
         return None
 
     def state_spec(self) -> StateSpec | tuple | None:

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from dataclasses import replace
 
-from .base import Block
+from .base import Block, NormedSum
 from .linear import settle
 from .registry import build_part, register_block
 
@@ -94,7 +94,7 @@ class OutputNormBlock(Block):
         from ..kernels import ops
         dtype = self.runtime.dtype
         if delta is not None:                                   # a block of another arrangement came before
-            if isinstance(delta, ops.SplitSum):
+            if hasattr(delta, "add_onto"):
                 delta.add_onto(h)
             else:
                 ops.add_inplace(h, delta)
@@ -107,5 +107,52 @@ class OutputNormBlock(Block):
         return h, None
 
 
+class SandwichNormBlock(Block):
+    """h += post1(mixer(pre1(h))); h += post2(feed_forward(pre2(h))): a norm in front of each sublayer and another on
+    its output.  The normed output is not added here: it is handed on as a ``NormedSum``, so that the norm in front of
+    the next sublayer (of this block, of the next block, or the model's last norm) adds it and norms the sum in one pass
+    over the row.  A layer without a feed-forward (``feed_forward`` None) has the first half only.
+    params: mixer_norm, mixer_post_norm, ffn_norm, ffn_post_norm (the norms' tensor names after the layer's prefix),
+    mixer_prefix, ffn_prefix."""
+
+    def __init__(self, spec, runtime, layer=None, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        px = spec.prefix
+
+        def norm(name):
+            return build_part("norm", replace(layer.norm, prefix=px, params={**dict(layer.norm.params), "name": name}), runtime)
+
+        self.norm1, self.norm1b = norm(p.get("mixer_norm", "norm1")), norm(p.get("mixer_post_norm", "norm1b"))
+        self.mixer = build_part("mixer", replace(layer.mixer, prefix=px + p.get("mixer_prefix", "mix") + "."),
+                                runtime, position=position)
+        self.ffn = self.norm2 = self.norm2b = None
+        if layer.feed_forward is not None:
+            self.norm2, self.norm2b = norm(p.get("ffn_norm", "norm2")), norm(p.get("ffn_post_norm", "norm2b"))
+            self.ffn = build_part("feed_forward", replace(layer.feed_forward, prefix=px + p.get("ffn_prefix", "mlp") + "."), runtime)
+
+    def parts(self):
+        return [part for part in (self.norm1, self.mixer, self.norm1b, self.norm2, self.ffn, self.norm2b) if part is not None]
+
+    def tensors(self):
+        return [t for part in self.parts() for t in part.tensors()]
+
+    def bind(self, weights):
+        for part in self.parts():
+            part.bind(weights)
+
+    def kernel_modules(self):
+        return tuple(m for part in self.parts() for m in part.kernel_modules())
+
+    def forward(self, h, delta, ctx, cache):
+        x = self.norm1.forward(h, settle(h, delta, self.norm1), write_sum=True)
+        delta = NormedSum(self.mixer.forward(x, ctx, cache), self.norm1b)
+        if self.ffn is not None:
+            x = self.norm2.forward(h, settle(h, delta, self.norm2), write_sum=True)
+            delta = NormedSum(self.ffn.forward(x, ctx), self.norm2b)
+        return h, delta
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("sandwich_norm", SandwichNormBlock)
 register_block("output_norm", OutputNormBlock)

@@ -36,7 +36,8 @@ class TokenEmbedding(Part):
 
 class OutputHead(Part):
     """params: vocab_size, hidden_size, tied (True, False, or None: tied iff the head's tensor is absent),
-    name, tied_to (name of the embedding table)."""
+    name, tied_to (name of the embedding table), scale (logits are multiplied by it; default 1), softcap (c > 0: logits
+    become c * tanh(logits / c) after the scale; default 0: none)."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -45,6 +46,8 @@ class OutputHead(Part):
         self.tied = spec.params.get("tied")
         self.name = self.prefix + spec.params.get("name", "lm_head.weight")
         self.tied_to = spec.params["tied_to"]
+        self.scale = float(spec.params.get("scale", 1.0))
+        self.softcap = float(spec.params.get("softcap", 0.0) or 0.0)
         self.weight = None
 
     def tensors(self):
@@ -59,10 +62,10 @@ class OutputHead(Part):
             self.weight = weights[self.name]
 
     def kernel_modules(self):
-        return linear_modules(self.runtime.dtype)
+        return ("elementwise", *linear_modules(self.runtime.dtype))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return linear(x, self.weight)
+        return ops.scale_softcap(linear(x, self.weight), self.scale, self.softcap)
 
 
 register_embedding("token", TokenEmbedding)

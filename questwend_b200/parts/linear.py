@@ -24,6 +24,7 @@ import os
 import torch
 
 from ..kernels import ops
+from .base import NormedSum
 
 
 def kernel_modules(dtype: torch.dtype) -> tuple:
@@ -131,6 +132,9 @@ def linear_onto(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor):
 def settle(h: torch.Tensor, delta, norm=None):
     """What a block hands its norm: ``delta`` as it is if the norm can add it, else added onto ``h`` (returns None)."""
     if isinstance(delta, ops.SplitSum) and not getattr(norm, "adds_split_sums", False):
+        delta.add_onto(h)
+        return None
+    if isinstance(delta, NormedSum) and not (getattr(norm, "adds_normed_sums", False) and type(delta.norm) is type(norm)):
         delta.add_onto(h)
         return None
     return delta

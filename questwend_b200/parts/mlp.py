@@ -55,39 +55,52 @@ class GatedMLP(FeedForward):
 
 
 class BiasedMLP(FeedForward):
-    """Ungated: down( act(up(x) + b_up) ) + b_down.
-    params: hidden_size, intermediate_size, activation (one of ``ops.ACTIVATIONS``), names (optional overrides)."""
+    """Ungated: down( act(up(x) + b_up) ) + b_down, or without the biases: down(act(up(x))).
+    params: hidden_size, intermediate_size, activation (one of ``ops.ACTIVATIONS``; one with learned numbers of its own,
+    as "xielu" has, reads them from the tensor ``act``), biases (default True), names (optional overrides)."""
 
-    NAMES = {"up": "up", "up_bias": "up.b", "down": "down", "down_bias": "down.b"}
+    NAMES = {"up": "up", "up_bias": "up.b", "down": "down", "down_bias": "down.b", "act": "act"}
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.hidden = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
         self.activation = str(spec.params["activation"])
+        self.biases = bool(spec.params.get("biases", True))
         if self.activation not in ops.ACTIVATIONS:
             raise ValueError(f"feed-forward '{self.prefix}': unknown activation '{self.activation}'; known: "
                              f"{', '.join(ops.ACTIVATIONS)}")
+        self.n_act_params = ops.ACTIVATION_PARAMS.get(self.activation, 0)
         self.names = {**self.NAMES, **dict(spec.params.get("names", {}))}
+        self.b_up = self.b_down = self.act_params = None
 
     def tensors(self):
         n, px = self.names, self.prefix
-        return [TensorSpec(px + n["up"], (self.inter, self.hidden), MATRIX), TensorSpec(px + n["up_bias"], (self.inter,), VECTOR),
-                TensorSpec(px + n["down"], (self.hidden, self.inter), MATRIX), TensorSpec(px + n["down_bias"], (self.hidden,), VECTOR)]
+        out = [TensorSpec(px + n["up"], (self.inter, self.hidden), MATRIX), TensorSpec(px + n["down"], (self.hidden, self.inter), MATRIX)]
+        if self.biases:
+            out += [TensorSpec(px + n["up_bias"], (self.inter,), VECTOR), TensorSpec(px + n["down_bias"], (self.hidden,), VECTOR)]
+        if self.n_act_params:
+            out.append(TensorSpec(px + n["act"], (self.n_act_params,), VECTOR))
+        return out
 
     def bind(self, weights):
         n, px = self.names, self.prefix
         self.w_up, self.w_down = weights[px + n["up"]], weights[px + n["down"]]
-        self.b_up = weights[px + n["up_bias"]].to(torch.float32).contiguous()
-        self.b_down = weights[px + n["down_bias"]].to(torch.float32).contiguous()
+        if self.biases:
+            self.b_up = weights[px + n["up_bias"]].to(torch.float32).contiguous()
+            self.b_down = weights[px + n["down_bias"]].to(torch.float32).contiguous()
+        if self.n_act_params:
+            self.act_params = weights[px + n["act"]].to(torch.float32).contiguous()
 
     def kernel_modules(self):
         return ("elementwise", *linear_modules(self.runtime.dtype))
 
     def forward(self, x, ctx):
-        act = ops.bias_act(linear(x, self.w_up), self.b_up, self.activation, self.runtime.dtype)
-        return ops.bias_act(linear(act, self.w_down), self.b_down, "none", torch.float32)
+        act = ops.bias_act(linear(x, self.w_up), self.b_up, self.activation, self.runtime.dtype, params=self.act_params)
+        out = linear(act, self.w_down)
+        return ops.bias_act(out, self.b_down, "none", torch.float32) if self.biases else out
 
 
 register_feed_forward("gated_mlp", GatedMLP)
 register_feed_forward("biased_mlp", BiasedMLP)
+register_feed_forward("plain_mlp", BiasedMLP)        # the same part under the name a plan without biases reads better with

@@ -1,5 +1,6 @@
 """Mixers that carry a state of fixed size from token to token instead of keys and values: the state-space
-recurrence of Mamba-2 and the gated delta rule with a decay per key channel.  Both keep, per sequence, a 32-bit
+recurrence of Mamba-2, the gated delta rule with a decay per key channel, and the recurrent block around a real-gated
+linear recurrent unit (one number of state per channel).  All keep, per sequence, a 32-bit
 state matrix per head and the last inputs of a short causal convolution, in the cache's per-slot state rows; a
 prompt and a single token run through the same kernels (``csrc/recurrent.cu``).  The projections are matrix
 products in the engine's dtype with 32-bit results; everything between them is 32-bit.
@@ -163,5 +164,72 @@ class GatedDeltaMixer(Mixer):
         return linear(g, self.w_out)
 
 
+class RGLRUMixer(Mixer):
+    """A recurrent block around a real-gated linear recurrent unit.  Two branches of ``width`` channels read the
+    mixer's input h: y = gelu_tanh(W_y h + b_y), and u = conv(W_x h + b_x), a causal convolution per channel with a
+    bias and no activation (zeros before a sequence's start).  The channels of u are cut into ``blocks`` equal parts;
+    per part b two gates r = sigmoid(A_b u_b + a_b) and i = sigmoid(I_b u_b + i_b) with square matrices.  Per channel
+    log a = -``sharpness`` * r * softplus(lam), S = a S + sqrt(1 - a^2) * i * u from S = 0, the first token like every
+    other; the output is W_o (S * y).  Gates, decays and the state are 32-bit.
+
+    params: hidden_size, width, blocks, conv (taps), sharpness (default 8), names (optional overrides).
+    State per sequence: the convolution's last taps - 1 inputs [taps - 1, width] and S [width]."""
+
+    NAMES = {"y": "y", "y_bias": "y.b", "x": "x", "x_bias": "x.b", "conv": "conv", "conv_bias": "conv.b",
+             "decay_gate": "ra", "decay_gate_bias": "ra.b", "input_gate": "ri", "input_gate_bias": "ri.b", "lam": "lam",
+             "out": "o"}
+
+    def __init__(self, spec, runtime, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden, self.width = int(p["hidden_size"]), int(p["width"])
+        self.blocks, self.taps = int(p["blocks"]), int(p["conv"])
+        self.sharpness = float(p.get("sharpness", 8.0))
+        self.names = {**self.NAMES, **dict(p.get("names", {}))}
+        if self.blocks <= 0 or self.width % self.blocks:
+            raise ValueError(f"rglru '{self.prefix}': {self.width} channels cannot be cut into {self.blocks} equal blocks")
+        refusal = conv_taps_refusal(self.taps)
+        if refusal:
+            raise ValueError(f"rglru '{self.prefix}': {refusal}")
+
+    def tensors(self):
+        n, px, W, D, nb = self.names, self.prefix, self.width, self.hidden, self.blocks
+        bw = W // nb
+        return [TensorSpec(px + n["y"], (W, D), MATRIX), TensorSpec(px + n["y_bias"], (W,), VECTOR),
+                TensorSpec(px + n["x"], (W, D), MATRIX), TensorSpec(px + n["x_bias"], (W,), VECTOR),
+                TensorSpec(px + n["conv"], (W, self.taps), VECTOR), TensorSpec(px + n["conv_bias"], (W,), VECTOR),
+                TensorSpec(px + n["decay_gate"], (nb, bw, bw), MATRIX), TensorSpec(px + n["decay_gate_bias"], (nb, bw), VECTOR),
+                TensorSpec(px + n["input_gate"], (nb, bw, bw), MATRIX), TensorSpec(px + n["input_gate_bias"], (nb, bw), VECTOR),
+                TensorSpec(px + n["lam"], (W,), VECTOR), TensorSpec(px + n["out"], (D, W), MATRIX)]
+
+    def bind(self, weights):
+        n, px = self.names, self.prefix
+        # one projection for both branches: y | x
+        self.w_in = torch.cat([take_weight(weights, px + n["y"]), take_weight(weights, px + n["x"])], dim=0).contiguous()
+        self.w_out = weights[px + n["out"]]
+        self.b_y, self.b_x, self.conv_w, self.conv_b, self.lam = (
+            _f32(weights, px + n[k]) for k in ("y_bias", "x_bias", "conv", "conv_bias", "lam"))
+        self.w_decay_gate, self.w_input_gate = (weights[px + n[k]].contiguous() for k in ("decay_gate", "input_gate"))
+        self.b_decay_gate, self.b_input_gate = (_f32(weights, px + n[k]) for k in ("decay_gate_bias", "input_gate_bias"))
+
+    def kernel_modules(self):
+        return ("recurrent", "rglru", *linear_modules(self.runtime.dtype))
+
+    def state_spec(self):
+        return (StateSpec((self.taps - 1, self.width), torch.float32), StateSpec((self.width,), torch.float32))
+
+    def forward(self, x, ctx, cache):
+        tail, state = cache.state
+        W = self.width
+        proj = linear(x, self.w_in)                                   # y | x before their biases, 32-bit
+        u = ops.short_conv(proj, W, W, self.conv_w, self.conv_b, tail, ctx, activation=False, update_tail=cache.writable,
+                           in_bias=self.b_x)
+        r, i = ops.block_gates(u, self.w_decay_gate, self.b_decay_gate, self.w_input_gate, self.b_input_gate)
+        g = ops.rglru_scan(u, r, i, self.lam, proj, 0, self.b_y, state, ctx, self.sharpness, self.runtime.dtype,
+                           write_state=cache.writable)
+        return linear(g, self.w_out)
+
+
 register_mixer("mamba2", Mamba2Mixer)
+register_mixer("rglru", RGLRUMixer)
 register_mixer("gated_delta_channelwise", GatedDeltaMixer)

@@ -76,9 +76,10 @@ class BiasedMLP(FeedForward):
 
     def tensors(self):
         n, px = self.names, self.prefix
-        out = [TensorSpec(px + n["up"], (self.inter, self.hidden), MATRIX), TensorSpec(px + n["down"], (self.hidden, self.inter), MATRIX)]
-        if self.biases:
-            out += [TensorSpec(px + n["up_bias"], (self.inter,), VECTOR), TensorSpec(px + n["down_bias"], (self.hidden,), VECTOR)]
+        out = [TensorSpec(px + n["up"], (self.inter, self.hidden), MATRIX), TensorSpec(px + n["up_bias"], (self.inter,), VECTOR),
+               TensorSpec(px + n["down"], (self.hidden, self.inter), MATRIX), TensorSpec(px + n["down_bias"], (self.hidden,), VECTOR)]
+        if not self.biases:
+            out = [out[0], out[2]]
         if self.n_act_params:
             out.append(TensorSpec(px + n["act"], (self.n_act_params,), VECTOR))
         return out

@@ -75,6 +75,19 @@ def movudra_sizes(width=2048, repeats=2, window=4096, vocab=32768):
             "vocab": vocab, "width": width}
 
 
+def roritar_sizes(width=2048, repeats=2, window=1024, pool=16, vocab=32768):
+    """A Roritar configuration at sizes that resemble real layers: per repeat two recurrent layers (2,560 channels in 10
+    blocks of 256, 4 taps) and one attention layer (16 heads of 128 over 4 key/value heads, values of 128, a window of
+    1,024 tokens and blocks of 16, half of each head rotated), each with a dense feed-forward of 4 x width."""
+    mlp = {"kind": "dense", "ff": 4 * width}
+    rec = {"type": "rglru", "mixer": {"blocks": 10, "conv": 4, "width": width * 5 // 4}, "mlp": mlp}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"dim": 128, "heads": width // 128, "kv_heads": width // 512, "vdim": 128, "scale": 128 ** -0.5,
+                     "mask": {"size": window, "pool": pool}, "rot": {"base": 10000.0, "dims": 64}}}
+    return {"architecture": "Roritar", "layers": [rec, rec, att] * repeats, "norm": {"eps": 1e-5}, "vocab": vocab, "width": width,
+            "logit_scale": 1.0, "logit_softcap": 30.0}
+
+
 def qwen3_beside(width=2048, layers=6, vocab=32768):
     """The closest model the library had, at the same width, depth and vocabulary: Qwen3 layers with 16 heads of 128
     (8 key/value heads) and a gated feed-forward of 3 x width."""
@@ -385,15 +398,15 @@ def time_parts(engine, torch, rng, n_tokens: int, batch: int, prompt: int = 0, r
     return out
 
 
-def movudra_workload(torch, np, peaks, steps: int, warmup: int) -> dict:
-    """Prefill and decode of the Movudra design at real layer sizes (``movudra_sizes``), and of Qwen3 layers of the same
-    width, depth and vocabulary (``qwen3_beside``): tokens a second for a 2,048-token prompt and for graph-replayed
+def movudra_workload(torch, np, peaks, steps: int, warmup: int, designs=None) -> dict:
+    """Prefill and decode of a design at real layer sizes (``movudra_sizes``, ``roritar_sizes``), and of Qwen3 layers of the
+    same width, depth and vocabulary (``qwen3_beside``): tokens a second for a 2,048-token prompt and for graph-replayed
     decode steps at batch 1 and 8 after 1,024-token prompts, the decode steps against the HBM roofline of the matrices
     they must read, and the time of every kind of mixer and feed-forward alone in both kinds of step."""
     from questwend_b200.config.registry import config_from_dict
     from questwend_b200.engine.engine import Engine
     out = {}
-    for name, cfgd in (("movudra", movudra_sizes()), ("qwen3_same_size", qwen3_beside())):
+    for name, cfgd in (designs or (("movudra", movudra_sizes()), ("qwen3_same_size", qwen3_beside()))):
         engine = Engine.from_config(config_from_dict(cfgd), seed=0, dtype="bfloat16", max_tokens=8 * (PROMPT_LEN + 512) + 4096,
                                     max_seq_len=N_CTX, max_batch=9)
         rng = np.random.default_rng(1)
@@ -410,6 +423,112 @@ def movudra_workload(torch, np, peaks, steps: int, warmup: int) -> dict:
         point["parts_decode_b8"] = time_parts(engine, torch, rng, 1, 8, prompt=PROMPT_LEN)
         out[name] = point
         release(engine, torch)
+    return out
+
+
+def roritar_kernels(torch, np, peaks) -> dict:
+    """The Roritar design's own kernels alone at the sizes of ``roritar_sizes``, each beside the like kernel of a model the
+    library had, with the bytes or FLOPs it must move and the share of the measured peak that this comes to: the layer
+    norms (beside the RMS norms), the recurrence (beside Mamba-2's), its gates, and attention over window and blocks in a
+    2,048-token prompt and in decode steps (beside Qwen3's attention over the same number of visible keys)."""
+    from questwend_b200.cache.manager import CacheManager
+    from questwend_b200.engine.engine import StepEntry, build_step_context
+    from questwend_b200.kernels import ops
+    from questwend_b200.parts.base import KVSpec, StateSpec
+    dev, bf = torch.device("cuda:0"), torch.bfloat16
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=7):
+        times = []
+        for _ in range(reps + 3):
+            flush.zero_()                                         # L2 holds nothing of the last run
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3)
+        return statistics.median(times[3:])
+
+    def point(us, n_bytes=0, flops=0):
+        p = {"us": round(us, 1)}
+        if n_bytes:
+            p.update(gb_s=round(n_bytes / us / 1e3, 1), hbm_frac=round(n_bytes / (us * 1e-6) / hbm, 3))
+        if flops:
+            p.update(tflops=round(flops / us / 1e6, 1), tensor_frac=round(flops / (us * 1e-6) / tf, 3))
+        return p
+
+    out = {}
+    T, D, W = 2048, 2048, 2560
+    for rows in (T, 8):
+        h, y = torch.randn(rows, D, device=dev), torch.randn(rows, D, device=dev)
+        w = torch.ones(D, device=dev)
+        n = rows * D
+        out[f"layer_norm_onto_and_norm_{rows}"] = point(timed(lambda: ops.layernorm(h, w, 1e-5, bf, add=y, add_weight=w, write_sum=True)), 14 * n)
+        out[f"rms_norm_onto_then_cast_{rows}"] = point(timed(lambda: ops.rmsnorm_onto(h, y, w, 1e-5, bf)), 14 * n)
+        out[f"rms_norm_with_sum_{rows}"] = point(timed(lambda: ops.rmsnorm(h, w, 1e-5, bf, delta=y, write_sum=True)), 14 * n)
+    # the recurrences: one prompt of 2,048 tokens, and a step of 8 single tokens
+    for rows, B in ((T, 1), (8, 8)):
+        cache = CacheManager([(None, (StateSpec((3, W)), StateSpec((W,))), None), (None, (StateSpec((3, 4096 + 2048)), StateSpec((64, 64, 128))), None)],
+                             4096, 8, 4096, bf, dev)
+        slots = cache.open(B)
+        ctx = build_step_context(cache, [StepEntry(s, [0] * (rows // B), []) for s in slots], 10, dev)[0]
+        u, r, i = (torch.rand(rows, W, device=dev) for _ in range(3))
+        proj, lam, yb = torch.randn(rows, 2 * W, device=dev), torch.randn(W, device=dev), torch.zeros(W, device=dev)
+        tail, state = cache.unit_cache(0).state
+        out[f"rglru_scan_{rows}"] = point(timed(lambda: ops.rglru_scan(u, r, i, lam, proj, 0, yb, state, ctx, 8.0, bf)), rows * W * 18)
+        wg = torch.randn(10, 256, 256, device=dev).to(bf) * 0.05
+        bg = torch.zeros(10, 256, device=dev)
+        out[f"block_gates_{rows}"] = point(timed(lambda: ops.block_gates(u, wg, bg, wg, bg)), rows * W * 12 + 2 * wg.numel() * 2,
+                                           2 * 2 * rows * W * 256)
+        cw, cb = torch.randn(W, 4, device=dev), torch.zeros(W, device=dev)
+        out[f"short_conv_{rows}"] = point(timed(lambda: ops.short_conv(proj, W, W, cw, cb, tail, ctx, activation=False, in_bias=cb)), rows * W * 8)
+        # Mamba-2 beside it: 64 heads of 64, state 128, 8 groups (the sizes of movudra_sizes)
+        heads, vdim, ns, groups = 64, 64, 128, 8
+        xbc = torch.randn(rows, heads * vdim + 2 * groups * ns, device=dev)
+        dt = torch.randn(rows, heads, device=dev)
+        hv = torch.zeros(heads, device=dev)
+        st2 = cache.unit_cache(1).state[1]
+        out[f"mamba2_scan_{rows}"] = point(timed(lambda: ops.ssm_scan(xbc, dt, 0, hv, hv, hv, st2, ctx, heads, vdim, ns, groups)),
+                                           rows * (xbc.shape[1] + heads * vdim) * 4 + (2 * B * st2[0].numel() * 4 if rows == B else 0))
+    # attention: 16 heads of 128 over 4 key/value heads, window 1,024, blocks of 16
+    H, G, dim, window, pool = 16, 4, 128, 1024, 16
+    for label, n_new, B, prompt in (("prefill_2048", 2048, 1, 0), ("prefill_8192", 8192, 1, 0), ("decode_b8_at_4096", 1, 8, 4095),
+                                    ("decode_b8_at_32768", 1, 8, 32767)):
+        tokens, blocks = KVSpec(G, dim, window, value_dim=dim), KVSpec(G, dim, window, value_dim=dim, stride=pool)
+        plain = KVSpec(2 * G, dim, 0)           # Qwen3's attention beside it: 8 key/value heads, every key visible
+        n_ctx = prompt + n_new
+        cache = CacheManager([((tokens, blocks), None, None), (plain, None, None)], B * n_ctx + 64 * B, B, n_ctx + 64, bf, dev)
+        slots = cache.open(B)
+        if prompt:
+            build_step_context(cache, [StepEntry(s, [0] * prompt, []) for s in slots], 10, dev)
+            for s in slots:
+                cache.advance(s, prompt)
+        for unit in (cache.unit_cache(0), cache.unit_cache(0).more[0], cache.unit_cache(1)):
+            unit.k_pool.normal_()
+            unit.v_pool.normal_()
+        ctx = build_step_context(cache, [StepEntry(s, [0] * n_new, []) for s in slots], 10, dev)[0]
+        rows = B * n_new
+        u0, u1, u2 = cache.unit_cache(0), cache.unit_cache(0).more[0], cache.unit_cache(1)
+        q = torch.randn(rows, H, dim, device=dev).to(bf)
+        cs = torch.ones(rows, dim // 2, device=dev)
+        t0, t1, t2 = (ctx.page_tables[u.group_id] for u in (u0, u1, u2))
+        if n_new > 1:       # keys a query sees: up to `window` tokens and (position - window) / pool blocks; 4 FLOPs per key and value
+            seen = sum(min(p + 1, window) + max(0, (p - window + 1) // pool) for p in range(n_new))
+            full = n_new * (n_new + 1) // 2
+            out[f"window_pool_attention_{label}"] = point(timed(lambda: ops.pool_attention(q, u0.k_pool, u0.v_pool, u1.k_pool, u1.v_pool, t0, t1, ctx, cs, cs, 0.09, window, pool, False), reps=3),
+                                                          flops=4 * H * dim * seen)
+            out[f"qwen3_attention_{label}"] = point(timed(lambda: ops.attn_prefill(q, u2.k_pool, u2.v_pool, t2, ctx.cu_seqlens, ctx.pos0, ctx.max_new, 0.09), reps=3),
+                                                    flops=4 * H * dim * full)
+        else:               # a decode step reads the visible keys and values of every key/value head once
+            seen = min(n_ctx, window) + max(0, (n_ctx - window) // pool)
+            out[f"window_pool_attention_{label}"] = point(timed(lambda: ops.pool_attention(q, u0.k_pool, u0.v_pool, u1.k_pool, u1.v_pool, t0, t1, ctx, cs, cs, 0.09, window, pool, False)),
+                                                          B * G * seen * 2 * dim * 2)
+            out[f"qwen3_attention_{label}"] = point(timed(lambda: ops.attn_decode(q, u2.k_pool, u2.v_pool, t2, ctx.seq_len, 0.09, ctx.max_len)),
+                                                    B * 2 * G * n_ctx * 2 * dim * 2)
+        del cache
+        torch.cuda.empty_cache()
     return out
 
 
@@ -505,9 +624,10 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--model", default="8b", choices=sorted(MODELS) + ["movudra"],
-                    help="8b: the benchmark; 0.6b, 32b: its other workloads alone; movudra: the Movudra design at real layer "
-                         "sizes beside Qwen3 layers of the same width and depth")
+    ap.add_argument("--model", default="8b", choices=sorted(MODELS) + ["movudra", "roritar", "roritar-kernels"],
+                    help="8b: the benchmark; 0.6b, 32b: its other workloads alone; movudra, roritar: that design at real layer "
+                         "sizes beside Qwen3 layers of the same width and depth; roritar-kernels: its own kernels alone, each "
+                         "beside the like kernel of a model the library had")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64, the e2e run and the other models")
@@ -535,6 +655,17 @@ def main() -> int:
         print(json.dumps({"metric": "Movudra at real layer sizes beside Qwen3 layers of equal width and depth", "n_gpus": 1,
                           "dtype": "bf16", "data": "synthetic: seeded random weights and uniform random token ids",
                           "peaks": peak_source, "points": movudra_workload(torch, np, peaks, steps, warmup)}))
+        return 0
+    if args.model == "roritar":
+        designs = (("roritar", roritar_sizes()), ("qwen3_same_size", qwen3_beside()))
+        print(json.dumps({"metric": "Roritar at real layer sizes beside Qwen3 layers of equal width and depth", "n_gpus": 1,
+                          "dtype": "bf16", "data": "synthetic: seeded random weights and uniform random token ids",
+                          "peaks": peak_source, "points": movudra_workload(torch, np, peaks, steps, warmup, designs)}))
+        return 0
+    if args.model == "roritar-kernels":
+        print(json.dumps({"metric": "Roritar's kernels alone, each beside the like kernel of an earlier model", "n_gpus": 1,
+                          "dtype": "bf16", "data": "synthetic: random tensors of the sizes of roritar_sizes; L2 flushed between runs",
+                          "peaks": peak_source, "points": roritar_kernels(torch, np, peaks)}))
         return 0
     if args.model != "8b":                      # one of the other workloads alone, as a line of its own
         points = small_model_workload(torch, np, peaks) if args.model == "0.6b" else large_model_workload(torch, np, peaks)

@@ -8,7 +8,7 @@
 // and len / pool block rows instead of len keys.  Tokens that have left the window and whose block is not complete in
 // that sense are not seen at all.  Tokens and blocks share one softmax.  window = 0: plain causal attention, no blocks.
 //
-// Keys and values may have different sizes (dim, vdim; multiples of 16 up to 256); query head h reads key/value head
+// Keys and values may have different sizes (dim, vdim; multiples of 8 up to 256); query head h reads key/value head
 // h / (H / G).  Per-head RMS norm of q and k with a weight shared by the heads, a rotation of the first `rdims` values of
 // q and k, and (rotate_v) a rotation of ALL of a value by its own position before it is cached, undone on each head's
 // output by the query's position (so the output depends on relative positions of values only).  Pairs of a rotation:
@@ -287,8 +287,8 @@ __global__ void pool_prefill_kernel(const T* __restrict__ q, const T* __restrict
 
 static int check_pool_sizes(const char* what, int H, int G, int dim, int vdim, int table_width, int window, int pool) {
     if (H <= 0 || G <= 0 || H % G) return qwb_fail(QWB_ERR_ARG, "%s: %d query heads are not a multiple of %d key/value heads", what, H, G);
-    if (dim <= 0 || dim % 16 || dim > QWB_POOL_MAX_DIM || vdim <= 0 || vdim % 16 || vdim > QWB_POOL_MAX_DIM)
-        return qwb_fail(QWB_ERR_ARG, "%s: key size %d or value size %d is not a multiple of 16 in [16, %d]", what, dim, vdim, QWB_POOL_MAX_DIM);
+    if (dim <= 0 || dim % 8 || dim > QWB_POOL_MAX_DIM || vdim <= 0 || vdim % 8 || vdim > QWB_POOL_MAX_DIM)
+        return qwb_fail(QWB_ERR_ARG, "%s: key size %d or value size %d is not a multiple of 8 in [8, %d]", what, dim, vdim, QWB_POOL_MAX_DIM);
     if (table_width <= 0 || window < 0 || pool < 0) return qwb_fail(QWB_ERR_ARG, "%s: bad table width %d, window %d or block size %d", what, table_width, window, pool);
     return 0;
 }

@@ -140,16 +140,18 @@ def pooled_window_attention(h, w, px, m, eps, round16=False, layout="halves"):
     v = turn(v, pos, base, vdim, layout)
     if round16:
         q, k, v = round_bf16(q), round_bf16(k), round_bf16(v)
+    nb = T // pool if pool else 0                  # a block's key and value: the means of its cached keys and values
+    kb = k[:nb * pool].reshape(nb, pool, G, dim).mean(axis=1) if nb else np.zeros((0, G, dim))
+    vb = v[:nb * pool].reshape(nb, pool, G, vdim).mean(axis=1) if nb else np.zeros((0, G, vdim))
+    if round16:
+        kb, vb = round_bf16(kb), round_bf16(vb)
     out = np.zeros((T, H, vdim))
     for i in range(T):
         first, blocks = visible(i, size, pool) if size else (0, 0)
         for hh in range(H):
             g = hh // (H // G)
-            keys = [k[b * pool:(b + 1) * pool, g].mean(axis=0) for b in range(blocks)] + list(k[first:i + 1, g])
-            vals = [v[b * pool:(b + 1) * pool, g].mean(axis=0) for b in range(blocks)] + list(v[first:i + 1, g])
-            keys, vals = np.array(keys), np.array(vals)
-            if round16 and blocks:
-                keys[:blocks], vals[:blocks] = round_bf16(keys[:blocks]), round_bf16(vals[:blocks])
+            keys = np.concatenate([kb[:blocks, g], k[first:i + 1, g]])
+            vals = np.concatenate([vb[:blocks, g], v[first:i + 1, g]])
             s = keys @ q[i, hh] * m["scale"]
             p = np.exp(s - s.max())
             out[i, hh] = (p / p.sum()) @ vals

@@ -338,6 +338,253 @@ extern "C" int qwb_pool_prefill(const void* q, const void* k_pool, const void* v
 }
 
 // ---------------------------------------------------------------------------------
+// prefill on the tensor cores (bfloat16, mma.sync m16n8k16): block = 64 queries of one (sequence, query head), 4 warps of
+// 16 rows; keys in tiles of 64 = one page of the block rows' pools, then of the tokens' pools, so a tile is one contiguous
+// piece of the cache.  Q, K and V tiles sit in shared memory with rows padded by 16 bytes (conflict-free ldmatrix); K and
+// V have two buffers, and the next tile is copied in (cp.async) while this one is multiplied.  Scores, maxima, sums and
+// the accumulator are 32-bit; probabilities are rounded to bfloat16 for the second product.  The normed outputs pass
+// through shared memory once, so that each value finds its partner when the head is turned back.
+// dim a multiple of 16, vdim of 8.
+// ---------------------------------------------------------------------------------
+#define PM_BQ 64
+#define PM_BK 64
+#define PM_PAD 8
+
+__device__ __forceinline__ void pm_ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const bf16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void pm_ldsm_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const bf16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void pm_mma(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// 16 bytes from global to shared memory; `bytes` 0 writes zeros (src must still be a valid address)
+__device__ __forceinline__ void pm_cp16(bf16* dst, const bf16* src, int bytes) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void pm_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void pm_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint32_t pm_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int NV>       // n-tiles of 8 value columns the accumulator has room for
+__global__ void __launch_bounds__(128)
+pool_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                        const bf16* __restrict__ pk_pool, const bf16* __restrict__ pv_pool, const int* __restrict__ page_table,
+                        const int* __restrict__ block_table, const int* __restrict__ cu_seqlens, const int* __restrict__ pos0,
+                        const float* __restrict__ cos_v, const float* __restrict__ sin_v, bf16* __restrict__ out, int H, int G,
+                        int dim, int vdim, int table_width, float scale, int window, int pool, int interleaved) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int ldq = dim + PM_PAD, ldv = vdim + PM_PAD;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);           // [64][ldq]
+    bf16* Kbuf = Qs + PM_BQ * ldq;                          // [2][64][ldq]
+    bf16* Vbuf = Kbuf + 2 * PM_BK * ldq;                    // [2][64][ldv]; at the end [64][vdim] floats
+
+    const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * PM_BQ;
+    const int t0 = cu_seqlens[b], n = cu_seqlens[b + 1] - t0;
+    if (q0 >= n) return;
+    const int g_kv = h / (H / G);
+    const int p0 = pos0[b];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nq = min(PM_BQ, n - q0);
+
+    for (int idx = tid; idx < PM_BQ * (dim / 8); idx += blockDim.x) {
+        const int r = idx / (dim / 8), c = (idx - r * (dim / 8)) * 8;
+        const bool in = r < nq;
+        pm_cp16(Qs + r * ldq + c, q + ((size_t)(t0 + (in ? q0 + r : 0)) * H + h) * dim + c, in ? 16 : 0);
+    }
+
+    float o[NV][4];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // rows gr and gr + 8 of the warp's 16
+    const int gr = lane >> 2, tq = lane & 3;
+    const int pos_a = p0 + q0 + warp * 16 + gr, pos_b = pos_a + 8;  // positions of the thread's two rows
+    const int seen_a = blocks_seen(pos_a, window, pool), seen_b = blocks_seen(pos_b, window, pool);
+
+    const int k_hi = p0 + q0 + nq - 1;                              // last key any query of the tile sees
+    const int k_lo = window > 0 ? max(0, p0 + q0 - window + 1) : 0;
+    const int n_blocks = blocks_seen(k_hi, window, pool);           // block rows the last query sees
+    const int nv_used = vdim / 8;
+    const int block_tiles = (n_blocks + PM_BK - 1) / PM_BK;
+    const int first_page = k_lo / PM_BK, token_tiles = k_hi / PM_BK - first_page + 1;
+    const int n_tiles = block_tiles + token_tiles;
+    const int* pages = page_table + (size_t)b * table_width;
+    const int* bpages = block_table ? block_table + (size_t)b * table_width : nullptr;
+
+    auto copy_tile = [&](int it, int stage) {                       // one commit group a tile
+        const bool blocks = it < block_tiles;
+        const int page = blocks ? it : first_page + (it - block_tiles);
+        const int rows = blocks ? min(PM_BK, n_blocks - page * PM_BK) : min(PM_BK, k_hi + 1 - page * PM_BK);
+        const size_t tile = ((size_t)(blocks ? bpages : pages)[page] * G + g_kv) * PM_BK;
+        const bf16* ks = (blocks ? pk_pool : k_pool) + tile * dim;
+        const bf16* vs = (blocks ? pv_pool : v_pool) + tile * vdim;
+        bf16* Kd = Kbuf + stage * PM_BK * ldq;
+        bf16* Vd = Vbuf + stage * PM_BK * ldv;
+        for (int idx = tid; idx < PM_BK * (dim / 8); idx += blockDim.x) {
+            const int r = idx / (dim / 8), c = (idx - r * (dim / 8)) * 8;
+            pm_cp16(Kd + r * ldq + c, ks + (size_t)(r < rows ? r : 0) * dim + c, r < rows ? 16 : 0);
+        }
+        for (int idx = tid; idx < PM_BK * (vdim / 8); idx += blockDim.x) {
+            const int r = idx / (vdim / 8), c = (idx - r * (vdim / 8)) * 8;
+            pm_cp16(Vd + r * ldv + c, vs + (size_t)(r < rows ? r : 0) * vdim + c, r < rows ? 16 : 0);
+        }
+        pm_commit();
+    };
+    copy_tile(0, 0);
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const bf16* Ks = Kbuf + (it & 1) * PM_BK * ldq;
+        const bf16* Vs = Vbuf + (it & 1) * PM_BK * ldv;
+        if (it + 1 < n_tiles) {                                     // the next tile into the other buffer (its last readers
+            copy_tile(it + 1, (it + 1) & 1);                        // passed the barrier at the end of the round before)
+            pm_wait<1>();
+        } else {
+            pm_wait<0>();
+        }
+        __syncthreads();
+        const bool blocks = it < block_tiles;
+        const int key0 = (blocks ? it : first_page + (it - block_tiles)) * PM_BK;
+
+        float s[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+        for (int d = 0; d < dim; d += 16) {
+            uint32_t a0, a1, a2, a3;
+            pm_ldsm_x4(a0, a1, a2, a3, Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldq + d + (lane >> 4) * 8);
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {                        // two tiles of 8 keys a load
+                uint32_t b0, b1, b2, b3;
+                pm_ldsm_x4(b0, b1, b2, b3, Ks + (j * 8 + (lane & 7) + (lane >> 4) * 8) * ldq + d + ((lane >> 3) & 1) * 8);
+                pm_mma(s[j], a0, a1, a2, a3, b0, b1);
+                pm_mma(s[j + 1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key0 + j * 8 + tq * 2 + (e & 1);
+                const int pos = e < 2 ? pos_a : pos_b;
+                const bool ok = blocks ? key < (e < 2 ? seen_a : seen_b) : (key <= pos && key <= k_hi && (window <= 0 || key > pos - window));
+                s[j][e] = ok ? s[j][e] * scale : -INFINITY;
+            }
+            mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float alpha0 = expf(m0 - base0), alpha1 = expf(m1 - base1);      // m = -inf gives 0
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            s[j][0] = expf(s[j][0] - base0); s[j][1] = expf(s[j][1] - base0);
+            s[j][2] = expf(s[j][2] - base1); s[j][3] = expf(s[j][3] - base1);
+            sum0 += s[j][0] + s[j][1];
+            sum1 += s[j][2] + s[j][3];
+        }
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1); sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+        sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1); sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+        l0 = l0 * alpha0 + sum0; l1 = l1 * alpha1 + sum1;
+        m0 = mn0; m1 = mn1;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) { o[j][0] *= alpha0; o[j][1] *= alpha0; o[j][2] *= alpha1; o[j][3] *= alpha1; }
+
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {                            // O += P V, 16 keys a step
+            const uint32_t a0 = pm_pack(s[2 * ks][0], s[2 * ks][1]), a1 = pm_pack(s[2 * ks][2], s[2 * ks][3]);
+            const uint32_t a2 = pm_pack(s[2 * ks + 1][0], s[2 * ks + 1][1]), a3 = pm_pack(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+            for (int j = 0; j < NV; j += 2) {
+                if (j < nv_used) {                                  // vdim / 8 may be odd: the second tile of a pair reads padding
+                    uint32_t b0, b1, b2, b3;                        // or the next row's start, and its result is never stored
+                    pm_ldsm_x4_trans(b0, b1, b2, b3, Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + j * 8 + (lane >> 4) * 8);
+                    pm_mma(o[j], a0, a1, a2, a3, b0, b1);
+                    if (j + 1 < NV) pm_mma(o[j + 1], a0, a1, a2, a3, b2, b3);
+                }
+            }
+        }
+        __syncthreads();                                            // this buffer may be copied into again
+    }
+
+    // the warp's 16 rows of normed output through shared memory (the V buffers are free), then turned back and stored
+    float* Os = reinterpret_cast<float*>(Vbuf) + (size_t)warp * 16 * vdim;
+    const float inv0 = 1.f / l0, inv1 = 1.f / l1;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        if (j < nv_used) {
+            const int col = j * 8 + tq * 2;
+            Os[gr * vdim + col] = o[j][0] * inv0; Os[gr * vdim + col + 1] = o[j][1] * inv0;
+            Os[(gr + 8) * vdim + col] = o[j][2] * inv1; Os[(gr + 8) * vdim + col + 1] = o[j][3] * inv1;
+        }
+    }
+    __syncwarp();
+    const int half = vdim >> 1;
+    for (int r = 0; r < 16; ++r) {
+        const int row = warp * 16 + r;
+        if (row >= nq) break;
+        const size_t t = (size_t)t0 + q0 + row;
+        const float* src = Os + r * vdim;
+        bf16* dst = out + (t * H + h) * vdim;
+        for (int c = lane * 2; c < vdim; c += 64) {
+            float x0 = src[c], x1 = src[c + 1];
+            if (cos_v) {
+                x0 = turned(src, c, vdim, cos_v + t * half, sin_v + t * half, interleaved, -1.f);
+                x1 = turned(src, c + 1, vdim, cos_v + t * half, sin_v + t * half, interleaved, -1.f);
+            }
+            *reinterpret_cast<uint32_t*>(dst + c) = pm_pack(x0, x1);
+        }
+    }
+}
+
+extern "C" int qwb_pool_prefill_mma_fits(int dtype, int dim, int vdim) {
+    const size_t smem = ((size_t)3 * PM_BQ * (dim + PM_PAD) + (size_t)2 * PM_BK * (vdim + PM_PAD)) * sizeof(bf16);
+    return dtype == QWB_DT_BF16 && dim > 0 && dim % 16 == 0 && vdim > 0 && vdim % 8 == 0 && dim <= QWB_POOL_MAX_DIM &&
+           vdim <= QWB_POOL_MAX_DIM && smem <= 220 * 1024;
+}
+
+extern "C" int qwb_pool_prefill_mma(const void* q, const void* k_pool, const void* v_pool, const void* pk_pool, const void* pv_pool,
+                                    const int* page_table, const int* block_table, const int* cu_seqlens, const int* pos0,
+                                    const float* cos_v, const float* sin_v, void* out, int B, int max_new, int H, int G, int dim,
+                                    int vdim, int table_width, float scale, int window, int pool, int interleaved, cudaStream_t stream) {
+    if (B <= 0 || max_new <= 0) return 0;
+    if (int rc = check_pool_sizes("pool_prefill_mma", H, G, dim, vdim, table_width, window, pool)) return rc;
+    if (!qwb_pool_prefill_mma_fits(QWB_DT_BF16, dim, vdim))
+        return qwb_fail(QWB_ERR_ARG, "pool_prefill_mma: keys of %d (a multiple of 16) and values of %d (of 8) that fit in shared memory", dim, vdim);
+    if (B > 65535 || H > 65535) return qwb_fail(QWB_ERR_ARG, "pool_prefill_mma: batch %d or heads %d above 65535", B, H);
+    if (window > 0 && pool > 0 && (!pk_pool || !pv_pool || !block_table)) return qwb_fail(QWB_ERR_ARG, "pool_prefill_mma: blocks without their pools");
+    for (const void* p : {q, k_pool, v_pool, (const void*)out})
+        if ((uintptr_t)p % 16) return qwb_fail(QWB_ERR_ARG, "pool_prefill_mma: a tensor is not 16-byte aligned");
+    const size_t smem = ((size_t)3 * PM_BQ * (dim + PM_PAD) + (size_t)2 * PM_BK * (vdim + PM_PAD)) * sizeof(bf16);
+    const dim3 grid((max_new + PM_BQ - 1) / PM_BQ, H, B);
+#define QWB_PM(NV)                                                                                                              \
+    do {                                                                                                                        \
+        if (smem > 48 * 1024) {                                                                                                 \
+            cudaError_t e = cudaFuncSetAttribute(pool_prefill_mma_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "pool_prefill_mma: %s", cudaGetErrorString(e));                 \
+        }                                                                                                                       \
+        qwb_launch(pool_prefill_mma_kernel<NV>, grid, 128, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, \
+                   (const bf16*)pk_pool, (const bf16*)pv_pool, page_table, block_table, cu_seqlens, pos0, cos_v, sin_v, (bf16*)out, H, G, \
+                   dim, vdim, table_width, scale, window, pool, interleaved);                                                   \
+    } while (0)
+    if (vdim <= 32) QWB_PM(4); else if (vdim <= 64) QWB_PM(8); else if (vdim <= 128) QWB_PM(16); else QWB_PM(32);
+#undef QWB_PM
+    return qwb_check_launch("pool_prefill_mma");
+}
+
+// ---------------------------------------------------------------------------------
 // decode: one new token per sequence (its position is len - 1).  Runs 0 .. block_runs - 1 walk the block rows, two pages
 // of 64 rows each; the runs after them walk the window's pages, counted from the page of the window's first key.  Which
 // rows a run holds follows from the sequence's own length alone.  Block = (run, key/value head and slice of its query

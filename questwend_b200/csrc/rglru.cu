@@ -10,7 +10,8 @@
 // digits when a is close to 1).  The read-out multiplies S by a second branch, gelu(y + bias) (tanh form), and is written in the
 // dtype of the product that follows.
 //
-//   block_gates      r and i for all tokens of a step: a tiled float product per (32 tokens, 64 outputs of one block)
+//   block_gates      r and i for all tokens of a step: a tiled float product per (64 tokens, 64 outputs of one block), or,
+//                    for up to 16 tokens, a warp per output channel that streams its row of the matrix
 //   rglru_scan       one thread per (sequence, channel) walks the sequence's tokens in order
 //   rglru_chunk_*    the same for long prompts in three passes: per chunk of tokens the product of its decays and its
 //                    sum from a zero state; the chunks' carries in order; the chunks again from their carries
@@ -21,27 +22,30 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-
 __device__ __forceinline__ float gelu_tanh_f(float v) { return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v))); }
 
 // ---------------------------------------------------------------------------------
-// gates: grid (ceil(T / 32), blocks * ceil(n / 64), 2); z = 0: r from Wa, z = 1: i from Wi.  256 threads; thread (ty, tx)
-// holds tokens 2 ty, 2 ty + 1 and outputs 4 tx .. 4 tx + 3 of the tile; k goes in steps of 32 through shared memory.
+// gates: grid (ceil(T / 64), blocks * ceil(n / 64), 2); z = 0: r from Wa, z = 1: i from Wi.  256 threads; thread (ty, tx)
+// holds tokens 4 ty .. 4 ty + 3 and outputs tx, tx + 16, tx + 32, tx + 48 of the tile (neighbouring lanes read neighbouring
+// rows of the weight tile: no bank conflicts); k goes in steps of 32 through shared memory.
 // ---------------------------------------------------------------------------------
+#define QWB_GATE_TILE_TOKENS 64
 template <typename TW>
 __global__ void __launch_bounds__(256)
 block_gates_kernel(const float* __restrict__ u, const TW* __restrict__ wa, const float* __restrict__ ba, const TW* __restrict__ wi,
                    const float* __restrict__ bi, float* __restrict__ r_out, float* __restrict__ i_out, int T, int C, int n) {
     pdl_wait();
     pdl_launch_dependents();
-    __shared__ float Us[32][33];
+    constexpr int TT = QWB_GATE_TILE_TOKENS;
+    __shared__ float Us[TT][33];
     __shared__ float Ws[64][33];
     const int tiles = (n + 63) / 64;
-    const int blk = blockIdx.y / tiles, o0 = (blockIdx.y % tiles) * 64, t0 = blockIdx.x * 32;
+    const int blk = blockIdx.y / tiles, o0 = (blockIdx.y % tiles) * 64, t0 = blockIdx.x * TT;
     const TW* W = (blockIdx.z ? wi : wa) + (size_t)blk * n * n;
     const float* bias = (blockIdx.z ? bi : ba) + (size_t)blk * n;
     float* out = blockIdx.z ? i_out : r_out;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    float acc[2][4] = {};
+    float acc[4][4] = {};
     for (int k0 = 0; k0 < n; k0 += 32) {
         __syncthreads();
-        for (int idx = tid; idx < 32 * 32; idx += 256) {
+        for (int idx = tid; idx < TT * 32; idx += 256) {
             const int tt = idx >> 5, kk = idx & 31;
             Us[tt][kk] = (t0 + tt < T && k0 + kk < n) ? u[(size_t)(t0 + tt) * C + blk * n + k0 + kk] : 0.f;
         }
@@ -52,23 +56,59 @@ block_gates_kernel(const float* __restrict__ u, const TW* __restrict__ wa, const
         __syncthreads();
 #pragma unroll 8
         for (int kk = 0; kk < 32; ++kk) {
-            const float a0 = Us[2 * ty][kk], a1 = Us[2 * ty + 1][kk];
+            float a[4], w[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float w = Ws[4 * tx + j][kk];
-                acc[0][j] += a0 * w;
-                acc[1][j] += a1 * w;
-            }
+            for (int i = 0; i < 4; ++i) { a[i] = Us[4 * ty + i][kk]; w[i] = Ws[tx + 16 * i][kk]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] += a[i] * w[j];
         }
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int t = t0 + 2 * ty + i;
+    for (int i = 0; i < 4; ++i) {
+        const int t = t0 + 4 * ty + i;
         if (t >= T) continue;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const int o = o0 + 4 * tx + j;
+            const int o = o0 + tx + 16 * j;
             if (o < n) out[(size_t)t * C + blk * n + o] = sigmoid_f(acc[i][j] + bias[o]);
+        }
+    }
+}
+
+// A step of a few tokens (up to 16 rows: decode steps): one warp per output channel and gate streams that channel's row of
+// the gate's matrix once, the lanes stride over k, and the tokens' sums are reduced over the warp in a fixed order.
+// grid (ceil(C / 8), 2), 8 warps.
+#define QWB_GATE_ROWS 16
+template <typename TW>
+__global__ void __launch_bounds__(256)
+block_gates_rows_kernel(const float* __restrict__ u, const TW* __restrict__ wa, const float* __restrict__ ba, const TW* __restrict__ wi,
+                        const float* __restrict__ bi, float* __restrict__ r_out, float* __restrict__ i_out, int T, int C, int n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.x * 8 + warp;
+    if (c >= C) return;
+    const int blk = c / n, o = c - blk * n;
+    const TW* W = (blockIdx.y ? wi : wa) + ((size_t)blk * n + o) * n;
+    const float* ub = u + (size_t)blk * n;
+    float acc[QWB_GATE_ROWS];
+#pragma unroll
+    for (int t = 0; t < QWB_GATE_ROWS; ++t) acc[t] = 0.f;
+    for (int k = lane; k < n; k += 32) {
+        const float w = to_f32(W[k]);
+#pragma unroll
+        for (int t = 0; t < QWB_GATE_ROWS; ++t)
+            if (t < T) acc[t] += w * ub[(size_t)t * C + k];
+    }
+    const float bias = (blockIdx.y ? bi : ba)[c];
+    float* out = blockIdx.y ? i_out : r_out;
+#pragma unroll
+    for (int t = 0; t < QWB_GATE_ROWS; ++t) {
+        if (t < T) {
+            const float v = warp_sum(acc[t]);
+            if (lane == 0) out[(size_t)t * C + c] = sigmoid_f(v + bias);
         }
     }
 }
@@ -80,7 +120,14 @@ extern "C" int qwb_block_gates(const float* u, const void* wa, const float* ba, 
     const int n = C / blocks;
     const long long gy = (long long)blocks * ((n + 63) / 64);
     if (gy > 65535) return qwb_fail(QWB_ERR_ARG, "block_gates: %d channels are too many", C);
-    dim3 grid((T + 31) / 32, (unsigned)gy, 2);
+    if (w_dtype != QWB_DT_BF16 && w_dtype != QWB_DT_F32) return qwb_fail(QWB_ERR_ARG, "block_gates: unknown dtype %d", w_dtype);
+    if (T <= QWB_GATE_ROWS) {
+        dim3 grid_rows((C + 7) / 8, 2);
+        if (w_dtype == QWB_DT_BF16) qwb_launch(block_gates_rows_kernel<bf16>, grid_rows, 256, 0, stream, u, (const bf16*)wa, ba, (const bf16*)wi, bi, r_out, i_out, T, C, n);
+        else qwb_launch(block_gates_rows_kernel<float>, grid_rows, 256, 0, stream, u, (const float*)wa, ba, (const float*)wi, bi, r_out, i_out, T, C, n);
+        return qwb_check_launch("block_gates_rows");
+    }
+    dim3 grid((T + QWB_GATE_TILE_TOKENS - 1) / QWB_GATE_TILE_TOKENS, (unsigned)gy, 2);
     if (w_dtype == QWB_DT_BF16) qwb_launch(block_gates_kernel<bf16>, grid, 256, 0, stream, u, (const bf16*)wa, ba, (const bf16*)wi, bi, r_out, i_out, T, C, n);
     else if (w_dtype == QWB_DT_F32) qwb_launch(block_gates_kernel<float>, grid, 256, 0, stream, u, (const float*)wa, ba, (const float*)wi, bi, r_out, i_out, T, C, n);
     else return qwb_fail(QWB_ERR_ARG, "block_gates: unknown dtype %d", w_dtype);

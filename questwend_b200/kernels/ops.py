@@ -935,10 +935,19 @@ def pool_update(k_pool, v_pool, pk_pool, pv_pool, page_table, block_table, ctx, 
           _i(max_blocks), _i(G), _i(dim), _i(vdim), _i(pool), _stream())
 
 
+def pool_prefill_mma_fits(dtype: torch.dtype, dim: int, vdim: int) -> bool:
+    """Whether prompts take the tensor-core kernel: bfloat16, keys in multiples of 16, values of 8, tiles that fit."""
+    if dtype != torch.bfloat16:
+        return False
+    return bool(_lookup("attention_pool", "qwb_pool_prefill_mma_fits")[1](_i(DT_BF16), _i(dim), _i(vdim)))
+
+
 def pool_attention(q: torch.Tensor, k_pool, v_pool, pk_pool, pv_pool, page_table, block_table, ctx, cos_v, sin_v,
-                   scale: float, window: int, pool: int, interleaved: bool) -> torch.Tensor:
+                   scale: float, window: int, pool: int, interleaved: bool, impl: str = "auto") -> torch.Tensor:
     """Attention of a step's tokens over their window and the block rows before it.  ``q`` [T, H, dim] in the cache's
-    dtype; returns [T, H * vdim] in that dtype, each head turned back by the query's position if ``cos_v`` is given."""
+    dtype; returns [T, H * vdim] in that dtype, each head turned back by the query's position if ``cos_v`` is given.
+    Steps of one token per sequence take the kernel that cuts the keys into runs; other steps the tensor-core kernel
+    where it fits (``impl`` "auto" or "mma"), else the plain one ("plain")."""
     _need(q, "q", k_pool.dtype, 3)
     T, H, dim = q.shape
     G, vdim = k_pool.shape[1], v_pool.shape[3]
@@ -957,6 +966,12 @@ def pool_attention(q: torch.Tensor, k_pool, v_pool, pk_pool, pv_pool, page_table
               _ptr(page_table), _ptr(block_table), _ptr(ctx.seq_len), _ptr(cos_v), _ptr(sin_v), _ptr(scratch), _ptr(out),
               _i(_dt(q.dtype)), _i(T), _i(H), _i(G), _i(dim), _i(vdim), _i(width), _f(scale), _i(window), _i(pool),
               _i(block_runs.value), _i(n_runs), _i(1 if interleaved else 0), _stream(), kernels=2)
+        return out
+    if impl == "mma" or (impl == "auto" and pool_prefill_mma_fits(q.dtype, dim, vdim)):
+        _call("attention_pool", "qwb_pool_prefill_mma", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(pk_pool), _ptr(pv_pool),
+              _ptr(page_table), _ptr(block_table), _ptr(ctx.cu_seqlens), _ptr(ctx.pos0), _ptr(cos_v), _ptr(sin_v), _ptr(out),
+              _i(ctx.n_seqs), _i(ctx.max_new), _i(H), _i(G), _i(dim), _i(vdim), _i(width), _f(scale), _i(window), _i(pool),
+              _i(1 if interleaved else 0), _stream())
         return out
     _call("attention_pool", "qwb_pool_prefill", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(pk_pool), _ptr(pv_pool), _ptr(page_table),
           _ptr(block_table), _ptr(ctx.cu_seqlens), _ptr(ctx.pos0), _ptr(cos_v), _ptr(sin_v), _ptr(out), _i(_dt(q.dtype)),

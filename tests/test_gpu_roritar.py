@@ -76,7 +76,7 @@ def test_xielu_and_capped_logits():
 @pytest.mark.parametrize("wdtype", DTYPES)
 def test_block_gates(blocks, n, wdtype):
     rng = np.random.default_rng(blocks * 100 + n)
-    for T in (1, 33, 70):
+    for T in (1, 16, 17, 70, 130):
         u = np.float32(rng.standard_normal((T, blocks * n))).astype(np.float64)
         wa, wi = (pr.round_bf16(rng.standard_normal((blocks, n, n))) for _ in range(2))
         ba, bi = (pr.round_bf16(rng.standard_normal((blocks, n))) for _ in range(2))
@@ -185,6 +185,35 @@ def test_attention_alone(entry, dtype):
     got = run_mixer(make_mixer(entry, dtype, w, width), dtype, xs, prompt_then_tokens(lens, extra))
     for g, x in zip(got, xs):
         assert close(g, plain_mixer(entry, x, w, dtype), dtype)
+
+
+@pytest.mark.parametrize("size, pool", [(0, 0), (1, 1), (5, 0), (63, 4), (64, 64), (65, 7), (100, 12), (200, 3)])
+@pytest.mark.parametrize("sizes", [dict(heads=4, kv_heads=2, dim=32, vdim=24), dict(heads=2, kv_heads=2, dim=64, vdim=64),
+                                   dict(heads=3, kv_heads=1, dim=16, vdim=136, layout="interleaved"),
+                                   dict(heads=2, kv_heads=1, dim=128, vdim=8)])
+def test_prompts_on_the_tensor_cores(sizes, size, pool, monkeypatch):
+    """bfloat16 steps of more than one token per sequence take the tensor-core kernel: against the plain implementation
+    and against the plain kernel, for windows and blocks around the key tile of 64, prompts that cross tiles, end
+    inside one or are a single token, whole, and continued in portions whose tiles start inside a page."""
+    entry = rh.attention(size=size, pool=pool, dims=8, **sizes)
+    width, dtype = 48, torch.bfloat16
+    w = rh.draw_weights(rh.config([(entry, None)], width=width), 14, sharp=1.5)
+    rng = np.random.default_rng(15)
+    lens = [330, 70, 1, 64]
+    xs = [pr.round_bf16(rng.standard_normal((n, width))) for n in lens]
+    refs = [plain_mixer(entry, x, w, dtype) for x in xs]
+    part = make_mixer(entry, dtype, w, width)
+    assert ops.pool_prefill_mma_fits(dtype, sizes["dim"], sizes["vdim"])
+    plans = ([lens], [[100, 3, 1, 63], [230, 67, 0, 1]], [[1, 1, 1, 1], [129, 2, 0, 2], [200, 67, 0, 61]])
+    fast = [run_mixer(part, dtype, xs, plan) for plan in plans]
+    real = ops.pool_attention
+    monkeypatch.setattr(ops, "pool_attention", lambda *a, **k: real(*a, **{**k, "impl": "plain"}))
+    slow = run_mixer(part, dtype, xs, plans[0])
+    for i, ref in enumerate(refs):
+        for got in fast:
+            assert close(got[i], ref, dtype), i
+        assert np.sqrt(np.mean((fast[0][i] - slow[i]) ** 2)) <= 0.01 * np.sqrt(np.mean(ref ** 2))
+    assert not ops.pool_prefill_mma_fits(torch.float32, 64, 64) and not ops.pool_prefill_mma_fits(dtype, 24, 16)
 
 
 def aligned_keys(w, n):

@@ -4,6 +4,9 @@
 //       EPI_ADD     y += product, y float                 (o and down projections onto the residual stream)
 //       EPI_SWIGLU  a = silu(gate) * up as bfloat16       (gate/up projection; W holds, for every 8 features, their 8 gate
 //                                                          rows and then their 8 up rows)
+//       EPI_XIELU   a = xIELU(y) as bfloat16              (the up projection of an ungated feed-forward: v > 0: c v^2 + v / 2,
+//                                                          v <= 0: d (e^v - 1 - v) + v / 2, with c = softplus(p) and
+//                                                          d = 1/2 + softplus(q) from two learned numbers on the device)
 //
 // One block per SM walks over 128 x BN tiles of y (tile t, t + blocks, ...).  Six warps with fixed roles:
 //   warp 0  one lane issues the TMA loads: per 64 columns of k a 128 x 64 tile of x and a BN x 64 tile of W, into a ring
@@ -32,6 +35,7 @@
 #define EPI_STORE 0
 #define EPI_ADD 1
 #define EPI_SWIGLU 2
+#define EPI_XIELU 3
 
 // ------------------------------------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -118,7 +122,7 @@ struct TcSmem {
 template <int BN, int EPI>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-               const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int* error) {
+               const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int* error, const float* __restrict__ act_params) {
     constexpr int STAGES = TcSmem<BN>::STAGES;
     constexpr uint32_t A_BYTES = TcSmem<BN>::A_BYTES, B_BYTES = TcSmem<BN>::B_BYTES;
     constexpr int COLS_PER_TILE = EPI == EPI_SWIGLU ? BN / 2 : BN;     // output columns of one tile
@@ -214,7 +218,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         // for the residual sum.  Two staging tiles per warp let the next chunk be prepared while the last one drains.
         const int lane_group = warp & 3;                      // a warp reads tensor-memory lanes [32 * (warp % 4), + 32)
         unsigned char* stage0 = staging + (size_t)lane_group * 2 * TC_STAGING_BYTES;
-        constexpr int CHUNKS = EPI == EPI_SWIGLU ? BN / 2 / 64 : BN / 32;
+        constexpr int CHUNKS = EPI == EPI_SWIGLU ? BN / 2 / 64 : (EPI == EPI_XIELU ? BN / 64 : BN / 32);
+        float act_up = 0.f, act_down = 0.f;
+        if (EPI == EPI_XIELU) {
+            const float p = act_params[0], q = act_params[1];
+            act_up = p > 20.f ? p : log1pf(expf(p));
+            act_down = 0.5f + (q > 20.f ? q : log1pf(expf(q)));
+        }
         int local = 0, stores = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_total && ok; tile += gridDim.x, ++local) {
@@ -256,6 +266,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                             my_row[(q * 2 + grp) ^ (lane & 7)] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                         }
                     }
+                } else if (EPI == EPI_XIELU) {
+                    // 64 features = 64 accumulator columns -> 64 bfloat16 = one 128-byte row
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        uint32_t v[32];
+                        tmem_ld32(taddr + ch * 64 + q * 32, v);
+#pragma unroll
+                        for (int grp = 0; grp < 4; ++grp) {
+                            uint32_t pk[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                float a[2];
+#pragma unroll
+                                for (int e = 0; e < 2; ++e) {
+                                    const float z = __uint_as_float(v[8 * grp + 2 * j + e]);
+                                    a[e] = z > 0.f ? act_up * z * z + 0.5f * z : act_down * (expm1f(z) - z) + 0.5f * z;
+                                }
+                                __nv_bfloat162 r = __floats2bfloat162_rn(a[0], a[1]);
+                                pk[j] = *reinterpret_cast<uint32_t*>(&r);
+                            }
+                            my_row[(q * 4 + grp) ^ (lane & 7)] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        }
+                    }
                 } else {
                     uint32_t v[32];
                     tmem_ld32(taddr + ch * 32, v);
@@ -270,7 +303,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) {
-                    const int col = n0 + ch * (EPI == EPI_SWIGLU ? 64 : 32);
+                    const int col = n0 + ch * ((EPI == EPI_SWIGLU || EPI == EPI_XIELU) ? 64 : 32);
                     if (EPI == EPI_ADD)
                         asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
                                      ::"l"(&map_out), "r"(smem_u32(st)), "r"(col), "r"(row0) : "memory");
@@ -327,11 +360,12 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int 
 }
 
 template <int BN, int EPI>
-static int launch_tc(const void* x, const void* W, void* out, int M, int N, int K, int w_rows, int* error, cudaStream_t stream) {
+static int launch_tc(const void* x, const void* W, void* out, int M, int N, int K, int w_rows, int* error, cudaStream_t stream,
+                     const float* act_params = nullptr) {
     CUtensorMap map_x, map_w, map_out;
     if (int rc = make_map(&map_x, x, M, K, TC_BM, "x")) return rc;
     if (int rc = make_map(&map_w, W, w_rows, K, BN, "W")) return rc;
-    if (int rc = make_map(&map_out, out, M, N, 32, "out", EPI != EPI_SWIGLU)) return rc;
+    if (int rc = make_map(&map_out, out, M, N, 32, "out", EPI != EPI_SWIGLU && EPI != EPI_XIELU)) return rc;
     const size_t smem = TcSmem<BN>::BYTES;
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "gemm_tc: %s", cudaGetErrorString(e));
@@ -344,7 +378,7 @@ static int launch_tc(const void* x, const void* W, void* out, int M, int N, int 
         if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
     }
     dim3 grid((unsigned)(n_tiles < n_sm ? n_tiles : n_sm));          // one block per SM, each walks over its tiles
-    e = qwb_launch(gemm_tc_kernel<BN, EPI>, grid, TC_THREADS, smem, stream, map_x, map_w, map_out, M, N, K, error);
+    e = qwb_launch(gemm_tc_kernel<BN, EPI>, grid, TC_THREADS, smem, stream, map_x, map_w, map_out, M, N, K, error, act_params);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "gemm_tc: launch failed: %s", cudaGetErrorString(e));
     return qwb_check_launch("gemm_tc");
 }
@@ -373,4 +407,17 @@ extern "C" int qwb_gemm_tc(const void* x, const void* W, void* out, int epilogue
     TC_CASE(64) TC_CASE(128) TC_CASE(256)
 #undef TC_CASE
     return qwb_fail(QWB_ERR_ARG, "gemm_tc: tile width %d is not 64, 128 or 256", tile_n);
+}
+
+// out bfloat16 [M, N] = xIELU(x W^T) with the activation's two numbers (float, on the device) in act_params.
+extern "C" int qwb_gemm_tc_xielu(const void* x, const void* W, void* out, const float* act_params, int M, int N, int K, int tile_n,
+                                 int* error, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8) return qwb_fail(QWB_ERR_ARG, "gemm_tc: inner size %d is not a multiple of 8", K);
+    if (N % 8) return qwb_fail(QWB_ERR_ARG, "gemm_tc: %d output columns are not a multiple of 8", N);
+    if ((uintptr_t)x % 16 || (uintptr_t)W % 16 || (uintptr_t)out % 16) return qwb_fail(QWB_ERR_ARG, "gemm_tc: operands must be 16-byte aligned");
+    if (!error || !act_params) return qwb_fail(QWB_ERR_ARG, "gemm_tc: an error word and the activation's numbers on the device are required");
+    if (tile_n == 128) return launch_tc<128, EPI_XIELU>(x, W, out, M, N, K, N, error, stream, act_params);
+    if (tile_n == 256) return launch_tc<256, EPI_XIELU>(x, W, out, M, N, K, N, error, stream, act_params);
+    return qwb_fail(QWB_ERR_ARG, "gemm_tc: tile width %d is not 128 or 256", tile_n);
 }

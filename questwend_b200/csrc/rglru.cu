@@ -77,31 +77,46 @@ block_gates_kernel(const float* __restrict__ u, const TW* __restrict__ wa, const
     }
 }
 
-// A step of a few tokens (up to 16 rows: decode steps): one warp per output channel and gate streams that channel's row of
-// the gate's matrix once, the lanes stride over k, and the tokens' sums are reduced over the warp in a fixed order.
-// grid (ceil(C / 8), 2), 8 warps.
+// A step of a few tokens (up to 16 rows: decode steps): a block takes 8 output channels of one gate block, a warp each.
+// The tokens' inputs of that gate block pass through shared memory once per block (512 values of k at a time); a warp
+// streams its channel's row of the gate's matrix once, the lanes stride over k, and the tokens' sums are reduced over the
+// warp in a fixed order.  grid (blocks * ceil(n / 8), 2), 8 warps.
 #define QWB_GATE_ROWS 16
+#define QWB_GATE_ROWS_K 512
 template <typename TW>
 __global__ void __launch_bounds__(256)
 block_gates_rows_kernel(const float* __restrict__ u, const TW* __restrict__ wa, const float* __restrict__ ba, const TW* __restrict__ wi,
                         const float* __restrict__ bi, float* __restrict__ r_out, float* __restrict__ i_out, int T, int C, int n) {
     pdl_wait();
     pdl_launch_dependents();
+    __shared__ float us[QWB_GATE_ROWS][QWB_GATE_ROWS_K];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int c = blockIdx.x * 8 + warp;
-    if (c >= C) return;
-    const int blk = c / n, o = c - blk * n;
-    const TW* W = (blockIdx.y ? wi : wa) + ((size_t)blk * n + o) * n;
+    const int groups = (n + 7) / 8;
+    const int blk = blockIdx.x / groups, o = (blockIdx.x % groups) * 8 + warp;
+    const TW* W = (blockIdx.y ? wi : wa) + ((size_t)blk * n + min(o, n - 1)) * n;
     const float* ub = u + (size_t)blk * n;
     float acc[QWB_GATE_ROWS];
 #pragma unroll
     for (int t = 0; t < QWB_GATE_ROWS; ++t) acc[t] = 0.f;
-    for (int k = lane; k < n; k += 32) {
-        const float w = to_f32(W[k]);
+    for (int k0 = 0; k0 < n; k0 += QWB_GATE_ROWS_K) {
+        const int kn = min(QWB_GATE_ROWS_K, n - k0);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < T * kn; idx += 256) {
+            const int t = idx / kn, kk = idx - t * kn;
+            us[t][kk] = ub[(size_t)t * C + k0 + kk];
+        }
+        __syncthreads();
+        if (o < n) {
+            for (int kk = lane; kk < kn; kk += 32) {
+                const float w = to_f32(W[k0 + kk]);
 #pragma unroll
-        for (int t = 0; t < QWB_GATE_ROWS; ++t)
-            if (t < T) acc[t] += w * ub[(size_t)t * C + k];
+                for (int t = 0; t < QWB_GATE_ROWS; ++t)
+                    if (t < T) acc[t] += w * us[t][kk];
+            }
+        }
     }
+    if (o >= n) return;
+    const int c = blk * n + o;
     const float bias = (blockIdx.y ? bi : ba)[c];
     float* out = blockIdx.y ? i_out : r_out;
 #pragma unroll
@@ -122,7 +137,7 @@ extern "C" int qwb_block_gates(const float* u, const void* wa, const float* ba, 
     if (gy > 65535) return qwb_fail(QWB_ERR_ARG, "block_gates: %d channels are too many", C);
     if (w_dtype != QWB_DT_BF16 && w_dtype != QWB_DT_F32) return qwb_fail(QWB_ERR_ARG, "block_gates: unknown dtype %d", w_dtype);
     if (T <= QWB_GATE_ROWS) {
-        dim3 grid_rows((C + 7) / 8, 2);
+        dim3 grid_rows((unsigned)(blocks * ((n + 7) / 8)), 2);
         if (w_dtype == QWB_DT_BF16) qwb_launch(block_gates_rows_kernel<bf16>, grid_rows, 256, 0, stream, u, (const bf16*)wa, ba, (const bf16*)wi, bi, r_out, i_out, T, C, n);
         else qwb_launch(block_gates_rows_kernel<float>, grid_rows, 256, 0, stream, u, (const float*)wa, ba, (const float*)wi, bi, r_out, i_out, T, C, n);
         return qwb_check_launch("block_gates_rows");

@@ -720,6 +720,22 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store", out:
     return out
 
 
+def gemm_tc_xielu(x: torch.Tensor, weight: torch.Tensor, params: torch.Tensor, tile_n: int = 256) -> torch.Tensor:
+    """bfloat16 xIELU(x W^T) [M, N] on the tcgen05 tensor cores, the activation in the product's epilogue; ``params``:
+    the activation's two learned numbers, float32 on the device."""
+    _need(x, "x", torch.bfloat16, 2)
+    _need(weight, "weight", torch.bfloat16, 2)
+    _need(params, "params", torch.float32, 1)
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K or params.numel() != 2:
+        raise KernelError(f"gemm_tc_xielu: x {tuple(x.shape)}, weight {tuple(weight.shape)}, {params.numel()} numbers")
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    _call("gemm_tc", "qwb_gemm_tc_xielu", _ptr(x), _ptr(weight), _ptr(out), _ptr(params), _i(M), _i(N), _i(K), _i(tile_n),
+          _ptr(gemm_tc_error_word(x.device)), _stream())
+    return out
+
+
 # ----------------------------------------------------------------------------- recurrent mixers
 CONV_MAX_TAPS = 8
 

@@ -151,3 +151,14 @@ def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out_dtype: torc
         if x.shape[0] >= TC_SWIGLU_MIN_ROWS and x.shape[1] >= TC_SWIGLU_MIN_INNER and x.shape[1] % 8 == 0:
             return ops.gemm_tc(x, weight_gate_up, epilogue="swiglu", tile_n=256)
     return ops.silu_mul(linear(x, weight_gate_up), out_dtype, interleave)
+
+
+def linear_act(x: torch.Tensor, weight: torch.Tensor, bias, activation: str, out_dtype: torch.dtype, params=None) -> torch.Tensor:
+    """act(x W^T + bias) [M, N] in ``out_dtype``.  Many bfloat16 rows of an activation that the tcgen05 product has as an
+    epilogue (xIELU without a bias) take that product, as the gated feed-forward does with its SiLU; everything else
+    is the product followed by the bias-and-activation kernel."""
+    M, K = x.shape
+    if (activation == "xielu" and bias is None and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16
+            and M >= TC_SWIGLU_MIN_ROWS and K >= TC_SWIGLU_MIN_INNER and K % 8 == 0 and weight.shape[0] % 8 == 0):
+        return ops.gemm_tc_xielu(x, weight, params)
+    return ops.bias_act(linear(x, weight), bias, activation, out_dtype, params=params)

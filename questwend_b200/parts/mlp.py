@@ -6,7 +6,7 @@ import torch
 from ..kernels import ops
 from ..weights.manifest import MATRIX, VECTOR, TensorSpec
 from .base import FeedForward, take_weight
-from .linear import kernel_modules as linear_modules, linear, linear_onto, linear_swiglu
+from .linear import kernel_modules as linear_modules, linear, linear_act, linear_onto, linear_swiglu
 from .registry import register_feed_forward
 
 
@@ -97,7 +97,7 @@ class BiasedMLP(FeedForward):
         return ("elementwise", *linear_modules(self.runtime.dtype))
 
     def forward(self, x, ctx):
-        act = ops.bias_act(linear(x, self.w_up), self.b_up, self.activation, self.runtime.dtype, params=self.act_params)
+        act = linear_act(x, self.w_up, self.b_up, self.activation, self.runtime.dtype, params=self.act_params)
         out = linear(act, self.w_down)
         return ops.bias_act(out, self.b_down, "none", torch.float32) if self.biases else out
 

@@ -72,7 +72,26 @@ def test_xielu_and_capped_logits():
     assert np.abs(ops.scale_softcap(dev(z), 0.5, 0.0).double().cpu().numpy() - 0.5 * z).max() <= 1e-6
 
 
-@pytest.mark.parametrize("blocks, n", [(1, 16), (3, 16), (4, 80), (2, 136), (16, 1), (5, 7)])
+@pytest.mark.parametrize("M, N, K", [(600, 264, 2048), (512, 1024, 2048), (1000, 72, 2056)])
+def test_xielu_in_the_tensor_core_products_epilogue(M, N, K):
+    """Many bfloat16 rows: the up projection's activation runs in the tcgen05 product's epilogue; the same numbers as the
+    library product followed by the activation kernel, up to the order of the 32-bit sums."""
+    from questwend_b200.parts.linear import linear_act
+    rng = np.random.default_rng(M + N)
+    x = dev(rng.standard_normal((M, K)), torch.bfloat16)
+    w = dev(rng.standard_normal((N, K)) / np.sqrt(K) * 2, torch.bfloat16)
+    params = dev(np.array([0.4, -0.3]))
+    before = ops.LAUNCHES[0]
+    got = linear_act(x, w, None, "xielu", torch.bfloat16, params=params)
+    assert ops.LAUNCHES[0] - before == 1                      # one kernel: the product with its epilogue
+    ops.gemm_tc_check(DEV)
+    ref = pr.xielu(x.double().cpu().numpy() @ w.double().cpu().numpy().T, 0.4, -0.3)
+    assert np.abs(got.double().cpu().numpy() - ref).max() <= 2.0 ** -7 * np.abs(ref).max()
+    two = ops.bias_act(torch.mm(x, w.t(), out_dtype=torch.float32), None, "xielu", torch.bfloat16, params=params)
+    assert np.abs((got.double() - two.double()).cpu().numpy()).max() <= 2.0 ** -7 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("blocks, n", [(1, 16), (3, 16), (4, 80), (2, 136), (16, 1), (5, 7), (1, 1040)])
 @pytest.mark.parametrize("wdtype", DTYPES)
 def test_block_gates(blocks, n, wdtype):
     rng = np.random.default_rng(blocks * 100 + n)
@@ -350,6 +369,24 @@ def test_whole_prompts_portions_batches_and_reuse(models, name, dtype):
     for i, ref in enumerate(refs):
         assert close(np.stack(rows[i]), ref, td), i
     assert eng.cache.slots.n_free == eng.max_batch and eng.cache.free_pages() == [g.pool.n for g in eng.cache._groups]
+
+
+def test_a_wide_model_through_the_tensor_core_paths(tmp_path):
+    """Width 2,048 and a prompt of 600 tokens: the feed-forward's activation runs in the tcgen05 product's epilogue, the
+    attention's prompt on the tensor cores, the recurrence in chunks; then single tokens."""
+    cfgd = rh.config([(rh.rglru(width=96, blocks=3, conv=4), rh.dense(ff=264)),
+                      (rh.attention(heads=4, kv_heads=2, dim=32, vdim=16, size=100, pool=9, dims=8), rh.dense(ff=72))],
+                     width=2048, vocab=128)
+    w = rh.draw_weights(cfgd, 41)
+    folder = rh.write_folder(str(tmp_path / "m"), cfgd, w)
+    tokens = np.random.default_rng(3).integers(0, 128, 606).tolist()
+    ref = pr.forward(tokens, w, cfgd, round16=True)
+    eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=2048, max_batch=2)
+    (s,) = eng.open_sequences(1)
+    rows = list(all_rows(eng, s, tokens[:600]))
+    for t in tokens[600:]:
+        rows.append(eng.step([StepEntry(s, [t], [0])]).double().cpu().numpy()[0])
+    assert close(np.stack(rows), ref, torch.bfloat16)
 
 
 def test_layer_by_layer(models):

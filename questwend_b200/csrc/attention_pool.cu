@@ -340,8 +340,9 @@ extern "C" int qwb_pool_prefill(const void* q, const void* k_pool, const void* v
 // ---------------------------------------------------------------------------------
 // prefill on the tensor cores (bfloat16, mma.sync m16n8k16): block = 64 queries of one (sequence, query head), 4 warps of
 // 16 rows; keys in tiles of 64 = one page of the block rows' pools, then of the tokens' pools, so a tile is one contiguous
-// piece of the cache.  Q, K and V tiles sit in shared memory with rows padded by 16 bytes (conflict-free ldmatrix); K and
-// V have two buffers, and the next tile is copied in (cp.async) while this one is multiplied.  Scores, maxima, sums and
+// piece of the cache.  Q, K and V tiles sit in shared memory with rows padded by 16 bytes (conflict-free ldmatrix); K has
+// two buffers, V one: the next tile's keys are copied in (cp.async) under this tile's work, its values under its own
+// scores and softmax.  Scores, maxima, sums and
 // the accumulator are 32-bit; probabilities are rounded to bfloat16 for the second product.  The normed outputs pass
 // through shared memory once, so that each value finds its partner when the head is turned back.
 // dim a multiple of 16, vdim of 8.
@@ -387,7 +388,8 @@ pool_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);           // [64][ldq]
     bf16* Kbuf = Qs + PM_BQ * ldq;                          // [2][64][ldq]
-    bf16* Vbuf = Kbuf + 2 * PM_BK * ldq;                    // [2][64][ldv]; at the end [64][vdim] floats
+    bf16* Vbuf = Kbuf + 2 * PM_BK * ldq;                    // [64][ldv]
+    float* Obuf = reinterpret_cast<float*>(Kbuf);           // at the end, over the key buffers: [64][vdim] floats
 
     const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * PM_BQ;
     const int t0 = cu_seqlens[b], n = cu_seqlens[b + 1] - t0;
@@ -421,35 +423,53 @@ pool_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     const int* pages = page_table + (size_t)b * table_width;
     const int* bpages = block_table ? block_table + (size_t)b * table_width : nullptr;
 
-    auto copy_tile = [&](int it, int stage) {                       // one commit group a tile
+    auto tile_source = [&](int it, const bf16** ks, const bf16** vs, int* rows) {
         const bool blocks = it < block_tiles;
         const int page = blocks ? it : first_page + (it - block_tiles);
-        const int rows = blocks ? min(PM_BK, n_blocks - page * PM_BK) : min(PM_BK, k_hi + 1 - page * PM_BK);
+        *rows = blocks ? min(PM_BK, n_blocks - page * PM_BK) : min(PM_BK, k_hi + 1 - page * PM_BK);
         const size_t tile = ((size_t)(blocks ? bpages : pages)[page] * G + g_kv) * PM_BK;
-        const bf16* ks = (blocks ? pk_pool : k_pool) + tile * dim;
-        const bf16* vs = (blocks ? pv_pool : v_pool) + tile * vdim;
+        *ks = (blocks ? pk_pool : k_pool) + tile * dim;
+        *vs = (blocks ? pv_pool : v_pool) + tile * vdim;
+    };
+    auto copy_keys = [&](int it, int stage) {                       // one commit group
+        const bf16 *ks, *vs;
+        int rows;
+        tile_source(it, &ks, &vs, &rows);
         bf16* Kd = Kbuf + stage * PM_BK * ldq;
-        bf16* Vd = Vbuf + stage * PM_BK * ldv;
         for (int idx = tid; idx < PM_BK * (dim / 8); idx += blockDim.x) {
             const int r = idx / (dim / 8), c = (idx - r * (dim / 8)) * 8;
             pm_cp16(Kd + r * ldq + c, ks + (size_t)(r < rows ? r : 0) * dim + c, r < rows ? 16 : 0);
         }
+        pm_commit();
+    };
+    auto copy_values = [&](int it) {                                // one commit group
+        const bf16 *ks, *vs;
+        int rows;
+        tile_source(it, &ks, &vs, &rows);
         for (int idx = tid; idx < PM_BK * (vdim / 8); idx += blockDim.x) {
             const int r = idx / (vdim / 8), c = (idx - r * (vdim / 8)) * 8;
-            pm_cp16(Vd + r * ldv + c, vs + (size_t)(r < rows ? r : 0) * vdim + c, r < rows ? 16 : 0);
+            pm_cp16(Vbuf + r * ldv + c, vs + (size_t)(r < rows ? r : 0) * vdim + c, r < rows ? 16 : 0);
         }
         pm_commit();
     };
-    copy_tile(0, 0);
+    // Keys have two buffers, values one: tile i + 1's keys are copied in under tile i's work, tile i + 1's values under its
+    // own scores and softmax (three blocks of threads then fit an SM instead of two).  Groups in the order of their
+    // commits: [Q, K0], V0, K1, V1, K2, ...
+    copy_keys(0, 0);
+    copy_values(0);
+    const float scale2 = scale * 1.4426950408889634f;               // scores in units of ln 2: exp2f below
+    const int warp_lo = p0 + q0 + warp * 16, warp_hi = warp_lo + 15;
+    const int warp_seen = blocks_seen(warp_lo, window, pool);       // block rows that every row of the warp sees
 
     for (int it = 0; it < n_tiles; ++it) {
         const bf16* Ks = Kbuf + (it & 1) * PM_BK * ldq;
-        const bf16* Vs = Vbuf + (it & 1) * PM_BK * ldv;
-        if (it + 1 < n_tiles) {                                     // the next tile into the other buffer (its last readers
-            copy_tile(it + 1, (it + 1) & 1);                        // passed the barrier at the end of the round before)
-            pm_wait<1>();
+        const bf16* Vs = Vbuf;
+        const bool more = it + 1 < n_tiles;
+        if (more) {                                                 // the next keys into the other buffer (its last readers
+            copy_keys(it + 1, (it + 1) & 1);                        // passed the barrier at the end of the round before)
+            pm_wait<2>();                                           // this tile's keys (and Q) are there
         } else {
-            pm_wait<0>();
+            pm_wait<1>();
         }
         __syncthreads();
         const bool blocks = it < block_tiles;
@@ -469,15 +489,20 @@ pool_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                 pm_mma(s[j + 1], a0, a1, a2, a3, b2, b3);
             }
         }
+        // a tile that every row of the warp sees whole needs no mask (most tiles of a long prompt)
+        const bool whole = blocks ? key0 + PM_BK <= warp_seen : (key0 + PM_BK - 1 <= warp_lo && (window <= 0 || key0 > warp_hi - window));
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int key = key0 + j * 8 + tq * 2 + (e & 1);
-                const int pos = e < 2 ? pos_a : pos_b;
-                const bool ok = blocks ? key < (e < 2 ? seen_a : seen_b) : (key <= pos && key <= k_hi && (window <= 0 || key > pos - window));
-                s[j][e] = ok ? s[j][e] * scale : -INFINITY;
+                bool ok = true;
+                if (!whole) {
+                    const int key = key0 + j * 8 + tq * 2 + (e & 1);
+                    const int pos = e < 2 ? pos_a : pos_b;
+                    ok = blocks ? key < (e < 2 ? seen_a : seen_b) : (key <= pos && key <= k_hi && (window <= 0 || key > pos - window));
+                }
+                s[j][e] = ok ? s[j][e] * scale2 : -INFINITY;
             }
             mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
             mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
@@ -486,12 +511,12 @@ pool_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
         const float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
-        const float alpha0 = expf(m0 - base0), alpha1 = expf(m1 - base1);      // m = -inf gives 0
+        const float alpha0 = exp2f(m0 - base0), alpha1 = exp2f(m1 - base1);    // m = -inf gives 0
         float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            s[j][0] = expf(s[j][0] - base0); s[j][1] = expf(s[j][1] - base0);
-            s[j][2] = expf(s[j][2] - base1); s[j][3] = expf(s[j][3] - base1);
+            s[j][0] = exp2f(s[j][0] - base0); s[j][1] = exp2f(s[j][1] - base0);
+            s[j][2] = exp2f(s[j][2] - base1); s[j][3] = exp2f(s[j][3] - base1);
             sum0 += s[j][0] + s[j][1];
             sum1 += s[j][2] + s[j][3];
         }
@@ -502,6 +527,8 @@ pool_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 #pragma unroll
         for (int j = 0; j < NV; ++j) { o[j][0] *= alpha0; o[j][1] *= alpha0; o[j][2] *= alpha1; o[j][3] *= alpha1; }
 
+        if (more) pm_wait<1>(); else pm_wait<0>();                  // this tile's values are there
+        __syncthreads();
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {                            // O += P V, 16 keys a step
             const uint32_t a0 = pm_pack(s[2 * ks][0], s[2 * ks][1]), a1 = pm_pack(s[2 * ks][2], s[2 * ks][3]);
@@ -516,11 +543,12 @@ pool_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                 }
             }
         }
-        __syncthreads();                                            // this buffer may be copied into again
+        __syncthreads();                                            // the values' buffer may be copied into again
+        if (more) copy_values(it + 1);
     }
 
-    // the warp's 16 rows of normed output through shared memory (the V buffers are free), then turned back and stored
-    float* Os = reinterpret_cast<float*>(Vbuf) + (size_t)warp * 16 * vdim;
+    // the warp's 16 rows of normed output through shared memory (the buffers are free), then turned back and stored
+    float* Os = Obuf + (size_t)warp * 16 * vdim;
     const float inv0 = 1.f / l0, inv1 = 1.f / l1;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
@@ -549,8 +577,15 @@ pool_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     }
 }
 
+// Q and two key buffers [64][dim + 8] and one value buffer [64][vdim + 8] of bfloat16; the outputs' [64][vdim] floats lie
+// over the key buffers at the end
+static size_t pm_smem_bytes(int dim, int vdim) {
+    const size_t keys = (size_t)2 * PM_BK * (dim + PM_PAD) * sizeof(bf16), outs = (size_t)PM_BQ * vdim * sizeof(float);
+    return (size_t)PM_BQ * (dim + PM_PAD) * sizeof(bf16) + (keys > outs ? keys : outs) + (size_t)PM_BK * (vdim + PM_PAD) * sizeof(bf16);
+}
+
 extern "C" int qwb_pool_prefill_mma_fits(int dtype, int dim, int vdim) {
-    const size_t smem = ((size_t)3 * PM_BQ * (dim + PM_PAD) + (size_t)2 * PM_BK * (vdim + PM_PAD)) * sizeof(bf16);
+    const size_t smem = pm_smem_bytes(dim, vdim);
     return dtype == QWB_DT_BF16 && dim > 0 && dim % 16 == 0 && vdim > 0 && vdim % 8 == 0 && dim <= QWB_POOL_MAX_DIM &&
            vdim <= QWB_POOL_MAX_DIM && smem <= 220 * 1024;
 }
@@ -567,7 +602,7 @@ extern "C" int qwb_pool_prefill_mma(const void* q, const void* k_pool, const voi
     if (window > 0 && pool > 0 && (!pk_pool || !pv_pool || !block_table)) return qwb_fail(QWB_ERR_ARG, "pool_prefill_mma: blocks without their pools");
     for (const void* p : {q, k_pool, v_pool, (const void*)out})
         if ((uintptr_t)p % 16) return qwb_fail(QWB_ERR_ARG, "pool_prefill_mma: a tensor is not 16-byte aligned");
-    const size_t smem = ((size_t)3 * PM_BQ * (dim + PM_PAD) + (size_t)2 * PM_BK * (vdim + PM_PAD)) * sizeof(bf16);
+    const size_t smem = pm_smem_bytes(dim, vdim);
     const dim3 grid((max_new + PM_BQ - 1) / PM_BQ, H, B);
 #define QWB_PM(NV)                                                                                                              \
     do {                                                                                                                        \

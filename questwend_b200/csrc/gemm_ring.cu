@@ -41,6 +41,7 @@
 #define GR_EPI_PLAIN 0                // y = product (+ residual)
 #define GR_EPI_SWIGLU 1               // rows of W: for every 8 features their 8 gate rows, then their 8 up rows
 #define GR_EPI_SPLIT 2                // equal shares of stages per block; y = [pieces][M][N], see above
+#define GR_EPI_XIELU 3                // act = xIELU(product) as bfloat16; `residual` points to the activation's two learned numbers
 
 __device__ __forceinline__ uint32_t gr_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void gr_mbar_init(uint64_t* bar, uint32_t count) {
@@ -322,6 +323,18 @@ gemm_ring_kernel(const bf16* x, const __grid_constant__ CUtensorMap map_w, const
                     else y[at] = onto + sum;
                 }
             }
+        } else if (EPI == GR_EPI_XIELU) {                    // v > 0: c v^2 + v / 2;  v <= 0: d (e^v - 1 - v) + v / 2
+            const float p = residual[0], q = residual[1];
+            const float c_up = p > 20.f ? p : log1pf(expf(p)), c_down = 0.5f + (q > 20.f ? q : log1pf(expf(q)));
+            for (int idx = threadIdx.x; idx < NT * 4 * 32; idx += GR_WARPS * 32) {
+                const int j = idx >> 7, r = (idx >> 5) & 3, ln = idx & 31;
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < GR_WARPS; ++w) v += mine[((w * NT + j) * 4 + r) * 32 + ln];
+                const int n = n0 + (ln >> 2) + ((r & 2) ? 8 : 0), m = 8 * j + 2 * (ln & 3) + (r & 1);
+                if (n < N && m < M)
+                    act[(size_t)m * N + n] = __float2bfloat16_rn(v > 0.f ? c_up * v * v + 0.5f * v : c_down * (expm1f(v) - v) + 0.5f * v);
+            }
         } else {                                             // rows g are gates, rows g + 8 the ups of the same features
             const int F = N >> 1, f0 = n0 >> 1;
             for (int idx = threadIdx.x; idx < NT * 2 * 32; idx += GR_WARPS * 32) {
@@ -450,4 +463,14 @@ extern "C" int qwb_gemm_ring_swiglu(const void* x, const void* W, void* act, int
     if (int rc = check_ring(x, W, M, K)) return rc;
     if (M <= 8) return launch_ring<1, GR_EPI_SWIGLU>((const bf16*)x, (const bf16*)W, nullptr, nullptr, (bf16*)act, M, 2 * F, K, error, stream);
     return launch_ring<2, GR_EPI_SWIGLU>((const bf16*)x, (const bf16*)W, nullptr, nullptr, (bf16*)act, M, 2 * F, K, error, stream);
+}
+
+// act bfloat16 [M, N] = xIELU(x W^T); params: the activation's two learned numbers, float, on the device.
+extern "C" int qwb_gemm_ring_xielu(const void* x, const void* W, void* act, const float* params, int M, int N, int K, int* error,
+                                   cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (!params) return qwb_fail(QWB_ERR_ARG, "gemm_ring: the activation's numbers are required");
+    if (int rc = check_ring(x, W, M, K)) return rc;
+    if (M <= 8) return launch_ring<1, GR_EPI_XIELU>((const bf16*)x, (const bf16*)W, params, nullptr, (bf16*)act, M, N, K, error, stream);
+    return launch_ring<2, GR_EPI_XIELU>((const bf16*)x, (const bf16*)W, params, nullptr, (bf16*)act, M, N, K, error, stream);
 }

@@ -11,7 +11,7 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
 
-#define QWB_CONV_MAX_TAPS 8
+#define QWB_CONV_MAX_TAPS 16
 
 // ---------------------------------------------------------------------------------
 // out[t, c] = act( bias[c] + sum_j w[c, j] * in(i - (taps - 1 - j), c) ),  i = the token's index in this step,

@@ -13,7 +13,7 @@ def head_dim_refusal(head_dim: int) -> str | None:
     return None
 
 
-CONV_MAX_TAPS = 8           # csrc/recurrent.cu: QWB_CONV_MAX_TAPS
+CONV_MAX_TAPS = 16          # csrc/recurrent.cu: QWB_CONV_MAX_TAPS
 SCAN_MAX_ROWS = 512         # rows of a recurrent state's column that one warp keeps in registers (csrc/recurrent.cu)
 LATENT_MAX_RANK = 512       # csrc/attention_latent.cu: QWB_LATENT_MAX_L
 LATENT_MAX_ROW = 1024       # ... QWB_LATENT_MAX_ROW

@@ -659,6 +659,20 @@ def gemm_ring_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def gemm_ring_xielu(x: torch.Tensor, weight: torch.Tensor, params: torch.Tensor) -> torch.Tensor:
+    """bfloat16 xIELU(x W^T) [M, N] for up to 16 rows by the ring kernel, the activation in its epilogue."""
+    _need(x, "x", torch.bfloat16, 2)
+    _need(weight, "weight", torch.bfloat16, 2)
+    _need(params, "params", torch.float32, 1)
+    M, K = x.shape
+    if weight.shape[1] != K or params.numel() != 2:
+        raise KernelError(f"gemm_ring_xielu: x is {tuple(x.shape)}, the weight {tuple(weight.shape)}, {params.numel()} numbers")
+    out = torch.empty((M, weight.shape[0]), dtype=torch.bfloat16, device=x.device)
+    _call("gemm_ring", "qwb_gemm_ring_xielu", _ptr(x), _ptr(weight), _ptr(out), _ptr(params), _i(M), _i(weight.shape[0]), _i(K),
+          _ptr(gemm_tc_error_word(x.device)), _stream())
+    return out
+
+
 _TC_ERROR: dict = {}    # device -> one int32 that a gemm_tc kernel sets when one of its waits gives up
 TC_EPILOGUES = {"store": 0, "add": 1, "swiglu": 2}
 
@@ -737,7 +751,7 @@ def gemm_tc_xielu(x: torch.Tensor, weight: torch.Tensor, params: torch.Tensor, t
 
 
 # ----------------------------------------------------------------------------- recurrent mixers
-CONV_MAX_TAPS = 8
+CONV_MAX_TAPS = 16
 
 
 def short_conv(x: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: torch.Tensor | None,

@@ -154,11 +154,14 @@ def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out_dtype: torc
 
 
 def linear_act(x: torch.Tensor, weight: torch.Tensor, bias, activation: str, out_dtype: torch.dtype, params=None) -> torch.Tensor:
-    """act(x W^T + bias) [M, N] in ``out_dtype``.  Many bfloat16 rows of an activation that the tcgen05 product has as an
-    epilogue (xIELU without a bias) take that product, as the gated feed-forward does with its SiLU; everything else
-    is the product followed by the bias-and-activation kernel."""
+    """act(x W^T + bias) [M, N] in ``out_dtype``.  bfloat16 rows of an activation that the own products have as an
+    epilogue (xIELU without a bias) take those, as the gated feed-forward does with its SiLU: the ring product for few
+    rows, the tcgen05 product for many; everything else is the product followed by the bias-and-activation kernel."""
     M, K = x.shape
-    if (activation == "xielu" and bias is None and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16
+    fused = activation == "xielu" and bias is None and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16
+    if fused and FEW_ROWS_KERNEL == "ring" and M <= ops.STREAM_M and K % 8 == 0 and _few_rows(M, weight):
+        return ops.gemm_ring_xielu(x, weight, params)
+    if (fused
             and M >= TC_SWIGLU_MIN_ROWS and K >= TC_SWIGLU_MIN_INNER and K % 8 == 0 and weight.shape[0] % 8 == 0):
         return ops.gemm_tc_xielu(x, weight, params)
     return ops.bias_act(linear(x, weight), bias, activation, out_dtype, params=params)

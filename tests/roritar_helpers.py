@@ -57,7 +57,7 @@ ONES = config([(rglru(width=16, blocks=1, conv=1), None),
                (attention(heads=1, kv_heads=1, dim=16, vdim=16, size=1, pool=1, dims=0), dense(ff=16)),
                (attention(heads=2, kv_heads=2, dim=8, vdim=8, size=0, pool=0, dims=8), None),
                (rglru(width=16, blocks=16, conv=2), dense(ff=16))],
-              width=16, vocab=32, eps=1e-6, loop=(0, 2, 1), logit_scale=None, logit_softcap=None)
+              width=16, vocab=37, eps=1e-6, loop=(0, 2, 1), logit_scale=None, logit_softcap=None)
 
 
 def draw_weights(cfgd, seed=0, slow_decay=False, sharp=1.0):

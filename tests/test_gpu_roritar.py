@@ -72,10 +72,11 @@ def test_xielu_and_capped_logits():
     assert np.abs(ops.scale_softcap(dev(z), 0.5, 0.0).double().cpu().numpy() - 0.5 * z).max() <= 1e-6
 
 
-@pytest.mark.parametrize("M, N, K", [(600, 264, 2048), (512, 1024, 2048), (1000, 72, 2056)])
+@pytest.mark.parametrize("M, N, K", [(600, 264, 2048), (512, 1024, 2048), (1000, 72, 2056), (1, 264, 2048), (8, 100, 64), (16, 384, 256)])
 def test_xielu_in_the_tensor_core_products_epilogue(M, N, K):
-    """Many bfloat16 rows: the up projection's activation runs in the tcgen05 product's epilogue; the same numbers as the
-    library product followed by the activation kernel, up to the order of the 32-bit sums."""
+    """bfloat16 rows: the up projection's activation runs in the epilogue of the tcgen05 product (many rows) or of the ring
+    product (up to 16); the same numbers as the library product followed by the activation kernel, up to the order of the
+    32-bit sums."""
     from questwend_b200.parts.linear import linear_act
     rng = np.random.default_rng(M + N)
     x = dev(rng.standard_normal((M, K)), torch.bfloat16)
@@ -158,7 +159,8 @@ def prompt_then_tokens(lens, extra):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("entry", [rh.rglru(), rh.rglru(width=80, blocks=1, conv=1), rh.rglru(width=272, blocks=2, conv=8),
-                                   rh.rglru(width=40, blocks=40, conv=2), rh.rglru(width=35, blocks=5, conv=3)])
+                                   rh.rglru(width=40, blocks=40, conv=2), rh.rglru(width=35, blocks=5, conv=3),
+                                   rh.rglru(width=24, blocks=2, conv=12)])
 def test_rglru_alone(entry, dtype):
     """Prompts in one step (one long enough for the chunked scan, one of a single token), then tokens one by one."""
     width = 48

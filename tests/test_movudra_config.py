@@ -70,7 +70,7 @@ def test_load_config_reads_the_shapes_of_a_folder(tmp_path):
 @pytest.mark.parametrize("path,value,word", [
     (("vocab",), None, "vocab"), (("width",), 0, "width"), (("norm", "eps"), -1.0, "eps"), (("layers",), [], "layers"),
     (("layers", 0, "type"), "lstm", "type"), (("layers", 0, "mixer", "heads"), 4, "kv_heads"),
-    (("layers", 0, "mixer", "conv"), 9, "conv"), (("layers", 1, "mixer", "rot", "dims"), 7, "dims"),
+    (("layers", 0, "mixer", "conv"), 17, "conv"), (("layers", 1, "mixer", "rot", "dims"), 7, "dims"),
     (("layers", 1, "mixer", "rot", "dims"), 10, "dims"), (("layers", 1, "mixer", "kv_rank"), 600, "kv_rank"),
     (("layers", 1, "mixer", "scale"), None, "scale"), (("layers", 1, "mlp", "router", "top"), 7, "top"),
     (("layers", 1, "mlp", "kind"), "sparse", "kind"), (("layers", 2, "mixer", "groups"), 4, "groups"),

@@ -39,7 +39,7 @@ def test_schedule_repeats_the_looped_run():
     (("layers", 0, "type"), "conv", "'type'"), (("layers", 1, "mixer", "blocks"), 5, "'width'"),
     (("layers", 0, "mixer", "kv_heads"), 3, "'heads'"), (("layers", 0, "mixer", "rot", "dims"), 7, "'dims'"),
     (("layers", 0, "mixer", "rot", "dims"), 32, "'dims'"), (("layers", 0, "mixer", "dim"), 20, "key sizes"),
-    (("layers", 0, "mixer", "vdim"), 264, "value sizes"), (("layers", 1, "mixer", "conv"), 9, "taps"),
+    (("layers", 0, "mixer", "vdim"), 264, "value sizes"), (("layers", 1, "mixer", "conv"), 17, "taps"),
     (("loop", "stop"), 6, "loop"), (("layers", 0, "mlp", "kind"), "moe", "'kind'"), (("logit_softcap",), -1.0, "logit_softcap"),
     (("layers", 0, "mixer", "rot", "layout"), "spiral", "'layout'")])
 def test_config_refuses_with_the_keys_name(path, value, word):

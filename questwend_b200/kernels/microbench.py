@@ -22,6 +22,8 @@ import torch
 
 from . import ops
 
+DEV = torch.device("cuda:0")
+
 L2_BYTES = 126 * 1024 * 1024
 
 
@@ -189,9 +191,40 @@ def bench_sample(B, V, temperature, top_k, top_p, iters, spread=3.0) -> dict:
             "bytes": B * V * 4, "GBps": B * V * 4 / us / 1e3}
 
 
+def bench_pool_attention(B, tokens, ctx, Hq, Hkv, dim, vdim, window, pool, iters, dtype=torch.bfloat16) -> dict:
+    """Attention over a window and pooled blocks: ``B`` sequences that bring ``tokens`` new tokens each after ``ctx``
+    cached ones (tokens = 1: the decode kernels; more: the prompt kernel).  Random keys, values and block rows."""
+    from ..cache.manager import CacheManager
+    from ..engine.engine import StepEntry, build_step_context
+    from ..parts.base import KVSpec
+    kinds = (KVSpec(Hkv, dim, window, value_dim=vdim), KVSpec(Hkv, dim, window, value_dim=vdim, stride=max(1, pool)))
+    n = ctx + tokens
+    cache = CacheManager([(kinds, None, None)], B * n + 64 * B, B, n + 64, dtype, DEV)
+    slots = cache.open(B)
+    if ctx:
+        build_step_context(cache, [StepEntry(s, [0] * ctx, []) for s in slots], 10, DEV)
+        for s in slots:
+            cache.advance(s, ctx)
+    rows, blocks = cache.unit_cache(0), cache.unit_cache(0).more[0]
+    for u in (rows, blocks):
+        u.k_pool.normal_()
+        u.v_pool.normal_()
+    step = build_step_context(cache, [StepEntry(s, [0] * tokens, []) for s in slots], 10, DEV)[0]
+    q = torch.randn(B * tokens, Hq, dim, device=DEV).to(dtype)
+    cs = torch.ones(B * tokens, vdim // 2, device=DEV)
+    t0, t1 = step.page_tables[rows.group_id], step.page_tables[blocks.group_id]
+    us = _time(lambda i: ops.pool_attention(q, rows.k_pool, rows.v_pool, blocks.k_pool, blocks.v_pool, t0, t1, step, cs, cs,
+                                            dim ** -0.5, window, pool, False), 1, iters, burst=3)
+    seen = sum(min(p + 1, window or p + 1) + (max(0, (p - window + 1) // pool) if window and pool else 0) for p in range(ctx, n))
+    return {"what": "pool_attention", "batch": B, "tokens": tokens, "ctx": ctx, "heads": Hq, "kv_heads": Hkv, "dim": dim,
+            "vdim": vdim, "window": window, "pool": pool, "us": us,
+            "tflops_of_visible_keys": 2 * B * Hq * (dim + vdim) * seen / us / 1e6,
+            "gb_s_of_visible_rows": (B * Hkv * (seen / tokens) * (dim + vdim) * q.element_size() / us / 1e3) if tokens == 1 else None}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn_decode", "attn_prefill", "rmsnorm", "rope", "decode_shapes", "sample"])
+    ap.add_argument("what", choices=["gemm", "attn_decode", "attn_prefill", "rmsnorm", "rope", "decode_shapes", "sample", "pool_attn"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
@@ -214,6 +247,9 @@ def main() -> int:
     ap.add_argument("--runs-target", type=int, default=0, help="tensor-core decode attention: about this many runs a sequence")
     ap.add_argument("--run-pages-max", type=int, default=0, help="tensor-core decode attention: at most this many pages a run")
     ap.add_argument("--fused", action="store_true", help="decode attention with the q/k norm, rotation and cache write inside")
+    ap.add_argument("--value-dim", type=int, default=0, help="pool_attn: size of a value (default: the head size)")
+    ap.add_argument("--window", type=int, default=1024, help="pool_attn: the window")
+    ap.add_argument("--pool", type=int, default=16, help="pool_attn: tokens per pooled block")
     args = ap.parse_args()
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     if args.what == "gemm":
@@ -227,6 +263,9 @@ def main() -> int:
     elif args.what == "attn_decode":
         print(json.dumps(bench_attn_decode(args.batch, args.ctx, args.heads, args.kv_heads, args.head_dim, args.iters, dtype, args.split,
                                            args.runs_target, args.run_pages_max, fused=args.fused, max_len=args.max_len)))
+    elif args.what == "pool_attn":
+        print(json.dumps(bench_pool_attention(args.batch, args.tokens, args.ctx if args.tokens == 1 else 0, args.heads, args.kv_heads,
+                                              args.head_dim, args.value_dim or args.head_dim, args.window, args.pool, args.iters, dtype)))
     elif args.what == "sample":
         print(json.dumps(bench_sample(args.batch, args.vocab, args.temp, args.top_k, args.top_p, args.iters)))
     elif args.what == "attn_prefill":

@@ -75,8 +75,12 @@ def model_info(config, dtype: str) -> dict:
     tensors = [t for t in model.tensors() if not (t.optional or t.ignored)]
     size = lambda dt: torch.empty((), dtype=dt).element_size()
     weight_bytes = sum(math.prod(t.shape) * size(held_dtype(t, compute, compute)) for t in tensors)
-    cache_bytes = sum((2 if kv.values else 1) * kv.n_kv_heads * kv.head_dim * size(compute)
-                      for kv, _, cache_of in model.cache_units() if kv is not None and cache_of is None)
+    # per token: a key row and (if the spec has values) a value row of its own size, per kind of row that a mixer keeps;
+    # a kind with a row per ``stride`` tokens counts that share
+    cache_bytes = sum(kv.n_kv_heads * (kv.head_dim + (kv.v_dim if kv.values else 0)) * size(compute) / max(1, kv.stride)
+                      for kvs, _, cache_of in model.cache_units() if kvs is not None and cache_of is None
+                      for kv in (kvs if isinstance(kvs, (tuple, list)) else (kvs,)))
+    cache_bytes = int(cache_bytes) if cache_bytes == int(cache_bytes) else round(cache_bytes, 1)
     state_bytes = sum(math.prod(sp.shape) * size(sp.dtype)
                       for _, st, cache_of in model.cache_units() if st is not None and cache_of is None
                       for sp in (st if isinstance(st, (tuple, list)) else (st,)))

@@ -120,3 +120,19 @@ def test_plain_activation_branches():
     out = pr.xielu(z, 0.3, -0.2)
     sp = lambda v: np.log1p(np.exp(v))
     assert np.allclose(out, [(0.5 + sp(-0.2)) * (np.exp(-2.0) - 1 + 2.0) - 1.0, 0.0, sp(0.3) * 9 + 1.5])
+
+
+def test_info_counts_rows_per_run_and_per_block(tmp_path, capsys):
+    import json
+    from questwend_b200 import cli
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(rh.MIXED))
+    assert cli.main(["--random", str(cfg), "--info"]) == 0
+    info = json.loads(capsys.readouterr().out)
+    assert info["config"]["architecture"] == "Roritar" and info["layers"] == 5
+    # per token: keys and values of every attention RUN (the looped layer counts three times), plus a block row's share
+    want = 2 * (24 + 16) * 2 * (1 + 1 / 5) + 3 * 3 * (16 + 40) * 2 * (1 + 1 / 12) + 1 * (8 + 8) * 2 * (1 + 1 / 7)
+    assert abs(info["memory"]["cache_bytes_per_token"] - want) < 0.1
+    # per sequence: convolution tails and states of every recurrent run
+    assert info["memory"]["state_bytes_per_sequence"] == 4 * 3 * ((4 - 1) * 48 + 48) + 4 * 3 * ((2 - 1) * 80 + 80)
+    assert info["parameters"] == sum(v.size for v in rh.draw_weights(rh.MIXED).values())

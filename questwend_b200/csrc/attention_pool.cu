@@ -628,6 +628,11 @@ extern "C" int qwb_pool_prefill_mma(const void* q, const void* k_pool, const voi
 // ---------------------------------------------------------------------------------
 #define QWB_POOL_GT 8      // query heads per block
 
+__device__ __forceinline__ void pool_cp16(void* dst, const void* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src));
+}
+
 // rows [first, end) of run `run` in its source (source 0: block rows, 1: tokens); empty if first >= end
 __device__ __forceinline__ void pool_run_rows(int len, int window, int pool, int block_runs, int run, int* source, int* first, int* end) {
     constexpr int RUN = QWB_POOL_RUN_PAGES * QWB_POOL_PAGE;
@@ -666,8 +671,9 @@ __global__ void pool_decode_kernel(const T* __restrict__ q, const T* __restrict_
     const int h0 = g * QG + g0;                         // first query head of this block
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    T* Kt = reinterpret_cast<T*>(smem_raw);             // [PG][dim]
-    T* Vt = Kt + (size_t)PG * dim;                      // [PG][vdim]
+    const int kld = dim + VEC;                          // a key row and 16 bytes: rows start in different banks
+    T* Kt = reinterpret_cast<T*>(smem_raw);             // [PG][dim + VEC]
+    T* Vt = Kt + (size_t)PG * kld;                      // [PG][vdim]
     float* qs = reinterpret_cast<float*>(Vt + (size_t)PG * vdim);   // [GT][dim], scaled
     float* sc = qs + GT * dim;                          // [GT][PG]
     float* m_s = sc + GT * PG;                          // [GT]
@@ -696,13 +702,16 @@ __global__ void pool_decode_kernel(const T* __restrict__ q, const T* __restrict_
         const int n_keys = min(PG, row_end - base);                   // rows of this page up to the run's end
         const size_t tile = (size_t)pages[base / PG] * G + g;
         __syncthreads();                                              // the last page's tiles are no longer read
-        {
+        {   // asynchronous copies: all of a thread's pieces are in flight together (loads through registers in a loop wait
+            // for one another: 16 round trips to memory a page)
             const uint4* ksrc = reinterpret_cast<const uint4*>(kp + tile * PG * dim);
             const uint4* vsrc = reinterpret_cast<const uint4*>(vp + tile * PG * vdim);
             uint4* kdst = reinterpret_cast<uint4*>(Kt);
             uint4* vdst = reinterpret_cast<uint4*>(Vt);
-            for (int i = tid; i < n_keys * dim / VEC; i += blockDim.x) kdst[i] = ksrc[i];
-            for (int i = tid; i < n_keys * vdim / VEC; i += blockDim.x) vdst[i] = vsrc[i];
+            for (int i = tid; i < n_keys * nchunk; i += blockDim.x) pool_cp16(kdst + i + i / nchunk, ksrc + i);    // row r starts at r * (nchunk + 1)
+            for (int i = tid; i < n_keys * vdim / VEC; i += blockDim.x) pool_cp16(vdst + i, vsrc + i);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
 
@@ -710,9 +719,8 @@ __global__ void pool_decode_kernel(const T* __restrict__ q, const T* __restrict_
             float s[GT];
 #pragma unroll
             for (int gi = 0; gi < GT; ++gi) s[gi] = 0.f;
-            const Vec16<T>* krow = reinterpret_cast<const Vec16<T>*>(Kt + (size_t)my_key * dim);
-            for (int c = 0; c < nchunk; ++c) {
-                const int ch = (my_key + c) % nchunk;                 // rotate: spread keys over the banks
+            const Vec16<T>* krow = reinterpret_cast<const Vec16<T>*>(Kt + (size_t)my_key * kld);
+            for (int ch = 0; ch < nchunk; ++ch) {                     // every lane the same piece of q: one broadcast read
                 float kf[VEC];
                 krow[ch].get(kf);
 #pragma unroll
@@ -846,7 +854,7 @@ static int launch_pool_decode(const void* q, const void* k_pool, const void* v_p
                               float* scratch, void* out, int B, int H, int G, int dim, int vdim, int table_width, float scale, int window,
                               int pool, int block_runs, int n_runs, int interleaved, cudaStream_t stream) {
     constexpr int GT = QWB_POOL_GT, PG = QWB_POOL_PAGE;
-    const size_t smem = (size_t)PG * (dim + vdim) * sizeof(T) + ((size_t)GT * dim + GT * PG + 3 * GT) * sizeof(float);
+    const size_t smem = (size_t)PG * (dim + vdim) * sizeof(T) + (size_t)PG * 16 + ((size_t)GT * dim + GT * PG + 3 * GT) * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(pool_decode_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "pool_decode: %s", cudaGetErrorString(e));
